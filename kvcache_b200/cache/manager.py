@@ -68,7 +68,7 @@ class CacheManager:
             for group in self.groups:
                 shape = (len(group.cache_ids), num_pages, group.spec.num_kv_heads, page_size, group.spec.head_dim)
                 group.k_pool = torch.zeros(shape, dtype=self.dtype, device=self.device)
-                group.v_pool = torch.zeros(shape, dtype=self.dtype, device=self.device)
+                group.v_pool = torch.zeros(shape[:-1] + (group.spec.v_head_dim,), dtype=self.dtype, device=self.device)
 
     # ---- requests ----------------------------------------------------------
     def admit(self) -> int:
@@ -161,7 +161,7 @@ class CacheManager:
     def kv_bytes_per_token(self) -> int:
         """Bytes of keys and values one token adds over all cache entries."""
         size = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * len(g.cache_ids) * g.spec.num_kv_heads * g.spec.head_dim * size for g in self.groups)
+        return sum(len(g.cache_ids) * g.spec.num_kv_heads * (g.spec.head_dim + g.spec.v_head_dim) * size for g in self.groups)
 
     # ---- views for a step --------------------------------------------------
     def table_rows(self, group: int, slots: Sequence[int]) -> np.ndarray:

@@ -140,7 +140,11 @@ def read_config_json(folder: str) -> Dict[str, Any]:
 
 
 def architecture_name(data: Mapping[str, Any], where: str = "config.json") -> str:
+    """The name under which the registry knows the model: `architectures[0]`, or a single `architecture`."""
+    single = data.get("architecture")
+    if isinstance(single, str) and single and data.get("architectures") is None:
+        return single
     archs = data.get("architectures")
     if not isinstance(archs, Sequence) or isinstance(archs, str) or len(archs) == 0 or not isinstance(archs[0], str):
-        raise ConfigError(f"{where}: 'architectures' must be a non-empty list of names")
+        raise ConfigError(f"{where}: 'architectures' must be a non-empty list of names (or 'architecture' one name)")
     return archs[0]

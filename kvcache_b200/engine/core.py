@@ -35,7 +35,8 @@ class EngineCore:
             num_pages = pages_for(options.max_cached_tokens, options.page_size)
         else:
             raise ValueError("give the cache a size: EngineOptions.num_pages or max_cached_tokens")
-        max_len = min(max_len, num_pages * options.page_size)
+        # A configuration without a longest length (positions come from a formula, not a learned table): the pool's size.
+        max_len = min(max_len, num_pages * options.page_size) if max_len else num_pages * options.page_size
         self.max_model_len = max_len
         self.model = load_model(folder, options.dtype, self.device, max_positions=max_len, strict=options.strict_weights)
         self.cache = CacheManager(self.model.cache_entries(), page_size=options.page_size, num_pages=num_pages,

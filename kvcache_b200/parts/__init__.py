@@ -1,13 +1,15 @@
 from .attention import GQAAttention
 from .base import (Block, FeedForward, LayerContext, Mixer, Norm, PagedKVSpec, PagedKVView, Part,
                    PositionEncoding, Rotation, StateSpec, StepBatch, StepPlan, StepPlanner, TORCH_DTYPES)
-from .block import PreNormBlock
-from .feedforward import GatedMLP
+from .block import PreNormBlock, SandwichBlock
+from .feedforward import GatedMLP, RoutedMLP
+from .latent_attention import LatentAttention
+from .stream import LoopEntry
 from .model import CacheEntry, DecoderModel, LayerCall
 from .norm import RMSNorm
-from .position import NoPositionEncoding, RotaryHalf
+from .position import NoPositionEncoding, RampScaling, RotaryHalf
 
 __all__ = ["GQAAttention", "Block", "FeedForward", "LayerContext", "Mixer", "Norm", "PagedKVSpec",
            "PagedKVView", "Part", "PositionEncoding", "Rotation", "StateSpec", "StepBatch", "StepPlan", "StepPlanner", "TORCH_DTYPES",
            "PreNormBlock", "GatedMLP", "CacheEntry", "DecoderModel", "LayerCall", "RMSNorm",
-           "NoPositionEncoding", "RotaryHalf"]
+           "NoPositionEncoding", "RotaryHalf", "RampScaling", "SandwichBlock", "RoutedMLP", "LatentAttention", "LoopEntry"]

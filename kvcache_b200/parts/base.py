@@ -39,6 +39,13 @@ class PagedKVSpec:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    # Size of a value row; None: as wide as a key.  0: the entry stores no values of its own - its mixer reads them out
+    # of the key rows (a latent that serves as key and as value), and the value pool is empty.
+    value_dim: Optional[int] = None
+
+    @property
+    def v_head_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)
@@ -54,7 +61,7 @@ class PagedKVView:
     """The cache one layer call reads and writes."""
     spec: PagedKVSpec
     k_pages: torch.Tensor            # [pages, num_kv_heads, page_size, head_dim]
-    v_pages: torch.Tensor
+    v_pages: torch.Tensor            # [pages, num_kv_heads, page_size, v_head_dim]
     block_table: torch.Tensor        # int32 [segments capacity, pages per request]; -1 where no page is held
     page_size: int
     writes: bool = True              # False: the call reads what another call wrote
@@ -123,6 +130,15 @@ class LayerContext:
     kv: Optional[PagedKVView] = None
     state: Any = None                # [slots, *StateSpec.shape], or a dict of such tensors by the states' names
     call_index: int = 0
+    embedded: Optional[torch.Tensor] = None   # float32 [T, width]: the embedding output, if a part of the model asked for it
+
+
+@dataclass
+class NormedDelta:
+    """What a block hands on instead of a plain delta when the delta is normalised before it is added:
+    h += post.norm(delta).  `Norm.add_norm` takes it wherever it takes a delta."""
+    delta: torch.Tensor
+    post: "Norm"
 
 
 class Part:
@@ -145,8 +161,11 @@ class Part:
 
 
 class Norm(Part):
-    def add_norm(self, h: torch.Tensor, delta: Optional[torch.Tensor], out: torch.Tensor,
-                 ctx: LayerContext, rows: Optional[torch.Tensor] = None) -> None:
+    def add_norm(self, h: torch.Tensor, delta, out: Optional[torch.Tensor],
+                 ctx: LayerContext, rows: Optional[torch.Tensor] = None, tail: Optional[torch.Tensor] = None) -> None:
+        """`delta`: None, a tensor, or a `NormedDelta` (normalised by its own norm before the add).  `out` None: only
+        the add.  `tail` (float32 rows as wide as h): `out` has twice the width and its right half receives `tail`
+        in the compute type, for a product over [normalised h | tail]."""
         raise NotImplementedError
 
     def fold_params(self) -> Optional[Tuple[torch.Tensor, float]]:
@@ -206,6 +225,16 @@ class FeedForward(Part):
         return False
 
     def forward_folded(self, h: torch.Tensor, h16: torch.Tensor, norm: "Norm", ctx: LayerContext) -> None:
+        raise NotImplementedError
+
+
+class StreamPart(Part):
+    """Acts on the residual stream between layers (`LayerCall.before`).  `forward` receives h, the delta that is still
+    pending, the context (with `ctx.embedded` if `needs_embedding`) and the integer of its call; it returns what is
+    pending afterwards."""
+    needs_embedding = False
+
+    def forward(self, h: torch.Tensor, pending, ctx: LayerContext, argument: int):
         raise NotImplementedError
 
 

@@ -22,6 +22,9 @@ class LayerCall:
     layer: int                 # index into the model's blocks
     cache: int                 # which cache entry the call uses
     writes_cache: bool = True  # False: reads what the writer of that entry stored in this step
+    # (index into the model's stream parts, an integer handed to it): a part that acts on the residual stream right
+    # before this call - what a pass over a run of layers does on entering it.
+    before: Optional[Tuple[int, int]] = None
 
 
 @dataclass(frozen=True)
@@ -34,7 +37,8 @@ class CacheEntry:
 class DecoderModel:
     def __init__(self, *, config: Any, dtype: str, vocab_size: int, width: int, embed_name: str,
                  head_name: Optional[str], blocks: Sequence[Block], schedule: Sequence[LayerCall],
-                 final_norm: Norm, position: Optional[PositionEncoding] = None, ignorable_tensors: Sequence[str] = ()):
+                 final_norm: Norm, position: Optional[PositionEncoding] = None, ignorable_tensors: Sequence[str] = (),
+                 stream_parts: Sequence[Any] = ()):
         self.config = config
         self.dtype_name = dtype
         self.dtype = TORCH_DTYPES[dtype]
@@ -44,6 +48,8 @@ class DecoderModel:
         self.schedule = list(schedule)
         self.final_norm = final_norm
         self.position = position
+        self.stream_parts = list(stream_parts)
+        self.keeps_embedding = any(getattr(part, "needs_embedding", False) for part in self.stream_parts)
         # Names (shell patterns) of tensors that checkpoints of this architecture may carry without the model using them.
         self.ignorable_tensors = tuple(ignorable_tensors)
         self._fold_cache: Dict[tuple, bool] = {}
@@ -53,6 +59,8 @@ class DecoderModel:
         for call in self.schedule:
             if not 0 <= call.layer < len(self.blocks):
                 raise ValueError(f"schedule names layer {call.layer}; the model has {len(self.blocks)} blocks")
+            if call.before is not None and not 0 <= call.before[0] < len(self.stream_parts):
+                raise ValueError(f"schedule names stream part {call.before[0]}; the model has {len(self.stream_parts)}")
         writers = {}
         for call in self.schedule:
             if call.writes_cache:
@@ -72,7 +80,7 @@ class DecoderModel:
         return self.head_name is None
 
     def _parts(self):
-        out = list(self.blocks) + [self.final_norm]
+        out = list(self.blocks) + [self.final_norm] + list(self.stream_parts)
         if self.position is not None:
             out.append(self.position)
         return out
@@ -106,6 +114,7 @@ class DecoderModel:
         """Bytes of weights a decode step reads once: every layer call's block, the final
         norm and the output matrix (embedding rows are a gather, not a stream)."""
         total = sum(self.blocks[c.layer].weight_bytes() for c in self.schedule)
+        total += sum(self.stream_parts[c.before[0]].weight_bytes() for c in self.schedule if c.before is not None)
         return total + self.final_norm.weight_bytes() + self.head.numel() * self.head.element_size()
 
     # ---- cache needs -------------------------------------------------------
@@ -129,6 +138,8 @@ class DecoderModel:
         may change the embedded rows behind the back of their rounded copy."""
         if self.position is not None and type(self.position).on_embed is not PositionEncoding.on_embed:
             return False
+        if self.stream_parts:
+            return False
         key = (id(kernels), num_rows, getattr(kernels, "fold_key", None))
         found = self._fold_cache.get(key)
         if found is None:
@@ -150,14 +161,21 @@ class DecoderModel:
             kernels.embed(self.embed, batch.token_ids, h, batch.token_src, batch.last_tokens, h16)
         else:
             kernels.embed(self.embed, batch.token_ids, h, batch.token_src, batch.last_tokens)
-        base = LayerContext(batch=batch, kernels=kernels, workspace=workspace)
+        embedded = None
+        if self.keeps_embedding:
+            # A second gather of the same rows: the embedding output, which parts between the layers read again.
+            embedded = workspace.buffer("model.embedded", (T, self.width), torch.float32)
+            kernels.embed(self.embed, batch.token_ids, embedded, batch.token_src, batch.last_tokens)
+        base = LayerContext(batch=batch, kernels=kernels, workspace=workspace, embedded=embedded)
         if self.position is not None:
             self.position.on_embed(h, base)
         pending = None
         for index, call in enumerate(self.schedule):
             ctx = LayerContext(batch=batch, kernels=kernels, workspace=workspace,
                                kv=cache.kv_view(call.cache, call.writes_cache),
-                               state=cache.state(call.cache), call_index=index)
+                               state=cache.state(call.cache), call_index=index, embedded=embedded)
+            if call.before is not None:
+                pending = self.stream_parts[call.before[0]].forward(h, pending, ctx, call.before[1])
             if fold:
                 self.blocks[call.layer].forward_folded(h, h16, ctx)
             else:

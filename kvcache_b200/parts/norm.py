@@ -6,7 +6,7 @@ from typing import Dict, Mapping, Optional
 import torch
 
 from ..weights.loader import TensorSpec
-from .base import LayerContext, Norm
+from .base import LayerContext, Norm, NormedDelta
 
 
 class RMSNorm(Norm):
@@ -30,7 +30,16 @@ class RMSNorm(Norm):
     def weight_bytes(self) -> int:
         return self.width * 4
 
-    def add_norm(self, h, delta, out, ctx: LayerContext, rows=None) -> None:
+    def add_norm(self, h, delta, out, ctx: LayerContext, rows=None, tail=None) -> None:
+        if isinstance(delta, NormedDelta) or out is None or tail is not None:
+            # h += post.norm(delta), then this norm: one launch for both sums of squares.
+            post = delta.post.fold_params() if isinstance(delta, NormedDelta) else None
+            if isinstance(delta, NormedDelta) and post is None:
+                raise ValueError("a delta can be normalised before the add only by a norm of the form v * rsqrt(mean(v^2) + eps) * w")
+            d = delta.delta if isinstance(delta, NormedDelta) else delta
+            ctx.kernels.norm_add_rmsnorm(h, d, post[0] if post else None, post[1] if post else 0.0, self.weight, self.eps, out,
+                                         rows, tail)
+            return
         ctx.kernels.add_rmsnorm(h, delta, self.weight, self.eps, out, rows)
 
     def fold_params(self):

@@ -120,3 +120,95 @@ class TorchKernels:
                 out[r] = int(torch.argmax(scores))
             else:
                 out[r] = int(torch.argmax(logits[r]))
+
+    # ---- operators of the latent-attention and routed feed-forward parts ------------------------------------------
+    def norm_add_rmsnorm(self, h, delta, delta_weight, delta_eps, weight, eps, out, rows=None, tail=None):
+        f = self.f
+        pick = (lambda t: t) if rows is None else (lambda t: t[rows.long()])
+        v = pick(h).to(f)
+        if delta is not None:
+            d = pick(delta).to(f)
+            if delta_weight is not None:
+                d = d * torch.rsqrt((d * d).mean(dim=-1, keepdim=True) + delta_eps) * delta_weight.to(f)
+            v = (pick(h) + d.to(torch.float32)).to(f) if f == torch.float32 else v + d
+        if rows is None and delta is not None:
+            h.copy_(v.to(torch.float32))
+        if out is None:
+            return
+        H = h.shape[1]
+        y = v if weight is None else v * torch.rsqrt((v * v).mean(dim=-1, keepdim=True) + eps) * weight.to(f)
+        out[:, :H] = y.to(out.dtype)
+        if tail is not None:
+            out[:, H:] = pick(tail).to(out.dtype)
+
+    def latent_norm_rope_append(self, proj, q_rank, kv_rank, rot_dim, q_weight, kv_weight, eps, cos, sin, batch, kv, cq_out):
+        f = self.f
+        norm = lambda v, w: v * torch.rsqrt((v * v).mean(dim=-1, keepdim=True) + eps) * w.to(f)
+        cq_out.copy_(norm(proj[:, :q_rank].to(f), q_weight).to(cq_out.dtype))
+        if not kv.writes:
+            return
+        pos = batch.positions.long()
+        c = norm(proj[:, q_rank:q_rank + kv_rank].to(f), kv_weight)
+        kr = proj[:, q_rank + kv_rank:q_rank + kv_rank + rot_dim].to(f).clone()
+        half = cos.shape[1]
+        co, si = cos[pos].to(f), sin[pos].to(f)
+        u, v = kr[:, :half].clone(), kr[:, half:2 * half].clone()
+        kr[:, :half], kr[:, half:2 * half] = u * co - v * si, v * co + u * si
+        page = kv.block_table[batch.row_segment.long(), pos // kv.page_size].long()
+        assert bool((page >= 0).all()), "append into a page the block table does not hold"
+        kv.k_pages[page, 0, pos % kv.page_size, :] = torch.cat([c, kr], dim=1).to(kv.k_pages.dtype)
+
+    def head_linear(self, x, w, out, rotate=None, gate=None):
+        f = self.f
+        T = x.shape[0]
+        H, N, K = w.shape
+        xs, os_ = x.shape[1] // H, out.shape[1] // H
+        xv = x.view(T, H, xs).to(f)
+        y = torch.einsum("thk,hnk->thn", xv[:, :, :K], w.to(f))
+        if gate is not None:
+            g, col = gate
+            y = y * torch.sigmoid(g[:, col:col + H * N].to(f).view(T, H, N))
+        res = out.view(T, H, os_)
+        res[:, :, :N] = y.to(out.dtype)
+        if rotate is not None:
+            cos, sin, positions = rotate
+            assert os_ - N == xs - K
+            half = cos.shape[1]
+            t = xv[:, :, K:].clone()
+            co, si = cos[positions.long()].to(f)[:, None, :], sin[positions.long()].to(f)[:, None, :]
+            u, v = t[..., :half].clone(), t[..., half:2 * half].clone()
+            t[..., :half], t[..., half:2 * half] = u * co - v * si, v * co + u * si
+            res[:, :, N:] = t.to(out.dtype)
+
+    def latent_attention(self, q, batch, kv, out, num_heads, value_dim, scale, workspace=None):
+        f = self.f
+        T, D = q.shape[0], kv.spec.head_dim
+        qf = q.to(f).view(T, num_heads, D)
+        window = kv.spec.window
+        result = torch.zeros(T, num_heads, value_dim, dtype=f, device=q.device)
+        for r in range(T):
+            p, seg = int(batch.positions[r]), int(batch.row_segment[r])
+            lo = max(0, p - window + 1) if window else 0
+            js = torch.arange(lo, p + 1, device=q.device)
+            pages = kv.block_table[seg, js // kv.page_size].long()
+            assert bool((pages >= 0).all()), "a needed key lies in a page the block table does not hold"
+            keys = kv.k_pages[pages, 0, js % kv.page_size, :].to(f)      # [n, D]
+            weights = torch.softmax((qf[r] @ keys.t()) * scale, dim=-1)   # [H, n]
+            result[r] = weights @ keys[:, :value_dim]
+        out.copy_(result.view(T, num_heads * value_dim).to(out.dtype))
+
+    def route_top(self, logits, chosen, share):
+        best, which = torch.topk(logits.to(self.f), chosen.shape[1], dim=-1)
+        chosen.copy_(which.to(torch.int32))
+        share.copy_(torch.softmax(best, dim=-1).to(torch.float32))
+
+    def routed_experts(self, x, w_up, w_down, chosen, share, out, activation, workspace=None):
+        assert activation == "relu2"
+        f = self.f
+        result = torch.zeros(x.shape[0], w_down.shape[1], dtype=f)
+        for r in range(x.shape[0]):
+            for s in range(chosen.shape[1]):
+                e = int(chosen[r, s])
+                a = torch.relu(w_up[e].to(f) @ x[r].to(f)) ** 2
+                result[r] += share[r, s].to(f) * (w_down[e].to(f) @ a.to(x.dtype).to(f))
+        out.copy_(result.to(out.dtype))
