@@ -14,14 +14,14 @@
 #include "common.cuh"
 
 #define ATTN_THREADS 128
-#define ATTN_MAX_D 512
+#define ATTN_MAX_D 1024
 
 template <typename T>
 __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
                                                const T* __restrict__ v_pages, const int* __restrict__ block_table,
                                                int table_stride, const int* __restrict__ positions,
                                                const int* __restrict__ row_segment, T* __restrict__ out, int Hq,
-                                               int Hkv, int D, int page_size, int window, float scale,
+                                               int Hkv, int D, int Dv, int page_size, int window, float scale,
                                                int* __restrict__ err) {
     pdl_wait();
     pdl_launch_dependents();
@@ -37,6 +37,9 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
     const int seg = row_segment[r];
     const int* table = block_table + (size_t)seg * table_stride;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    // Values as wide as the keys lie in a pool of their own; narrower ones (Dv < D) are the first Dv numbers of the key
+    // rows themselves (a latent that serves as key and as value), and `v_pages` is then the key pool.
+    const int v_stride = v_pages == k_pages ? D : Dv;
 
     const T* qr = q + ((size_t)r * Hq + h) * D;
     for (int d = threadIdx.x; d < D; d += blockDim.x) q_s[d] = to_f32<T>(qr[d]);
@@ -77,42 +80,67 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
 #pragma unroll
         for (int i = 0; i < DPT; ++i) {
             const int d = threadIdx.x + i * ATTN_THREADS;
-            if (d < D) {
+            if (d < Dv) {
                 float a = acc[i] * corr;
                 for (int t = 0; t < n; ++t) {
                     const int o = page_s[t];
-                    if (o >= 0) a += p_s[t] * to_f32<T>(v_pages[(size_t)o * D + d]);
+                    if (o >= 0) a += p_s[t] * to_f32<T>(v_pages[(size_t)o * v_stride + d]);
                 }
                 acc[i] = a;
             }
         }
         __syncthreads();
     }
-    T* orow = out + ((size_t)r * Hq + h) * D;
+    T* orow = out + ((size_t)r * Hq + h) * Dv;
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
         const int d = threadIdx.x + i * ATTN_THREADS;
-        if (d < D) orow[d] = from_f32<T>(l > 0.f ? acc[i] / l : 0.f);
+        if (d < Dv) orow[d] = from_f32<T>(l > 0.f ? acc[i] / l : 0.f);
     }
 }
 
 KVB_API int kvb_paged_attention_generic(int dtype, const void* q, const void* k_pages, const void* v_pages,
                                         const int* block_table, int table_stride, const int* positions,
                                         const int* row_segment, void* out, int T, int Hq, int Hkv, int D,
-                                        int page_size, int window, float scale, int* err, cudaStream_t stream) {
+                                        int page_size, int window, float scale, int* err, cudaStream_t stream);
+
+// The same where a row's value is the first `Dv` numbers of its key row (one pool): out is [T, Hq * Dv].
+KVB_API int kvb_paged_attention_shared(int dtype, const void* q, const void* k_pages, const int* block_table, int table_stride,
+                                       const int* positions, const int* row_segment, void* out, int T, int Hq, int Hkv, int D,
+                                       int Dv, int page_size, int window, float scale, int* err, cudaStream_t stream);
+
+static int launch_generic(int dtype, const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                          int table_stride, const int* positions, const int* row_segment, void* out, int T, int Hq, int Hkv,
+                          int D, int Dv, int page_size, int window, float scale, int* err, cudaStream_t stream) {
     if (T <= 0) return KVB_OK;
-    if (D > ATTN_MAX_D || D < 1 || Hkv < 1 || Hq % Hkv != 0) return KVB_ERR_SHAPE;
+    if (D > ATTN_MAX_D || D < 1 || Dv < 1 || Dv > D || Hkv < 1 || Hq % Hkv != 0) return KVB_ERR_SHAPE;
     const size_t smem = (size_t)(D + 2 * ATTN_THREADS + 33) * sizeof(float);
     dim3 grid(T, Hq);
     if (dtype == KVB_F32)
         kvb_launch(paged_attention_generic_kernel<float>, dim3(grid), dim3(ATTN_THREADS), smem, stream, 
             (const float*)q, (const float*)k_pages, (const float*)v_pages, block_table, table_stride, positions,
-            row_segment, (float*)out, Hq, Hkv, D, page_size, window, scale, err);
+            row_segment, (float*)out, Hq, Hkv, D, Dv, page_size, window, scale, err);
     else if (dtype == KVB_BF16)
         kvb_launch(paged_attention_generic_kernel<bf16>, dim3(grid), dim3(ATTN_THREADS), smem, stream, 
             (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, table_stride, positions,
-            row_segment, (bf16*)out, Hq, Hkv, D, page_size, window, scale, err);
+            row_segment, (bf16*)out, Hq, Hkv, D, Dv, page_size, window, scale, err);
     else
         return KVB_ERR_DTYPE;
     return kvb_launch_status();
+}
+
+KVB_API int kvb_paged_attention_generic(int dtype, const void* q, const void* k_pages, const void* v_pages,
+                                        const int* block_table, int table_stride, const int* positions,
+                                        const int* row_segment, void* out, int T, int Hq, int Hkv, int D,
+                                        int page_size, int window, float scale, int* err, cudaStream_t stream) {
+    if (v_pages == k_pages) return KVB_ERR_SHAPE;      // one pool for both is the other entry point's case
+    return launch_generic(dtype, q, k_pages, v_pages, block_table, table_stride, positions, row_segment, out, T, Hq, Hkv, D, D,
+                          page_size, window, scale, err, stream);
+}
+
+KVB_API int kvb_paged_attention_shared(int dtype, const void* q, const void* k_pages, const int* block_table, int table_stride,
+                                       const int* positions, const int* row_segment, void* out, int T, int Hq, int Hkv, int D,
+                                       int Dv, int page_size, int window, float scale, int* err, cudaStream_t stream) {
+    return launch_generic(dtype, q, k_pages, k_pages, block_table, table_stride, positions, row_segment, out, T, Hq, Hkv, D, Dv,
+                          page_size, window, scale, err, stream);
 }

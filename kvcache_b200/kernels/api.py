@@ -99,6 +99,24 @@ _SIGNATURES = {
         "kvb_paged_attention_generic": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
                                         _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                         _c_float, _c_void_p, _c_void_p],
+        "kvb_paged_attention_shared": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                                       _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
+    },
+    "latent": {
+        "kvb_norm_add_rmsnorm": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_float, _c_void_p, _c_void_p,
+                                 _c_void_p, _c_int, _c_int, _c_void_p],
+        "kvb_latent_norm_rope_append": [_c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
+                                        _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                                        _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p],
+        "kvb_head_linear": [_c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                            _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p],
+    },
+    "moe": {
+        "kvb_route_top": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+        "kvb_routed_plan": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+        "kvb_grouped_gemm": [_c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
+                             _c_int, _c_int, _c_int, _c_void_p],
+        "kvb_routed_combine": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     },
     "gemm_simt": {
         "kvb_gemm_simt": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
@@ -200,6 +218,8 @@ class CudaKernels(KernelSet):
         self._rope = _Library("rope_append")
         self._attn_generic = _Library("attention_generic")
         self._gemm_simt = _Library("gemm_simt")
+        self._latent = _Library("latent")
+        self._moe = _Library("moe")
         self._sampling = _Library("sampling")
         self._gemm_skinny = _Library("gemm_skinny")
         self._gemm_tc = _Library("gemm_tcgen05")
@@ -658,6 +678,114 @@ class CudaKernels(KernelSet):
             kv.block_table.shape[1], _ptr(batch.positions), _ptr(batch.row_segment), _ptr(out), T, num_heads,
             spec.num_kv_heads, spec.head_dim, kv.page_size, spec.window or 0, float(scale),
             _ptr(self.error_word), self._stream()), "paged_attention")
+
+    # ---- latent attention, normalised adds, routed feed-forward ----------------------------------------------
+    def norm_add_rmsnorm(self, h: torch.Tensor, delta: Optional[torch.Tensor], delta_weight: Optional[torch.Tensor],
+                         delta_eps: float, weight: Optional[torch.Tensor], eps: float, out: Optional[torch.Tensor],
+                         rows: Optional[torch.Tensor] = None, tail: Optional[torch.Tensor] = None) -> None:
+        """v = h + (delta_weight given: rmsnorm(delta; delta_weight, delta_eps), else delta); without `rows`, h = v.
+        out[:, :H] = rmsnorm(v; weight, eps), or v itself if `weight` is None; out[:, H:] = tail (float32 rows like h)
+        in out's type.  `rows`: only these rows, gathered into out, h untouched.  `out` None: only the add."""
+        if delta is None and out is None:
+            return
+        n, H = (out.shape[0] if out is not None else h.shape[0]), h.shape[1]
+        if out is not None and out.shape[1] != (2 * H if tail is not None else H):
+            raise KernelError(f"norm_add_rmsnorm: out{tuple(out.shape)} does not fit rows of {H}")
+        dtype = out.dtype if out is not None else delta.dtype
+        if delta is not None and delta.dtype != dtype:
+            raise KernelError("norm_add_rmsnorm: delta and out differ in type")
+        self._count("norm_add_rmsnorm")
+        _check(self._latent.kvb_norm_add_rmsnorm(_dtype_code(dtype), _ptr(h), _ptr(delta), _ptr(delta_weight), float(delta_eps),
+                                                 _ptr(weight), float(eps), _ptr(out), _ptr(rows), _ptr(tail), n, H, self._stream()),
+               "norm_add_rmsnorm")
+
+    def latent_norm_rope_append(self, proj: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, q_weight: torch.Tensor,
+                                kv_weight: torch.Tensor, eps: float, cos: torch.Tensor, sin: torch.Tensor, batch: StepBatch,
+                                kv: PagedKVView, cq_out: torch.Tensor) -> None:
+        """cq_out = rmsnorm(proj[:, :q_rank]; q_weight); if kv.writes, the cache row of every row's (request, position)
+        = [rmsnorm(proj[:, q_rank:q_rank + kv_rank]; kv_weight) | the next rot_dim columns rotated by the position]."""
+        T, P = proj.shape
+        if kv.spec.head_dim != kv_rank + rot_dim or kv.spec.num_kv_heads != 1:
+            raise KernelError("latent_norm_rope_append: the cache entry is not one row of kv_rank + rot_dim numbers per token")
+        self._count("latent_norm_rope_append")
+        _check(self._latent.kvb_latent_norm_rope_append(
+            _dtype_code(proj.dtype), _ptr(proj), P, q_rank, kv_rank, rot_dim, _ptr(q_weight), _ptr(kv_weight), float(eps),
+            _ptr(cos), _ptr(sin), cos.shape[1], cos.shape[0], _ptr(batch.positions), _ptr(batch.row_segment),
+            _ptr(kv.block_table), kv.block_table.shape[1], _ptr(kv.k_pages), kv.page_size, 1 if kv.writes else 0, _ptr(cq_out),
+            T, _ptr(self.error_word), self._stream()), "latent_norm_rope_append")
+
+    def head_linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rotate=None, gate=None) -> None:
+        """One product per head: with H, N, K = w.shape, xs = x.shape[1] / H, os = out.shape[1] / H,
+        out[t, h * os + n] = sum_k x[t, h * xs + k] * w[h, n, k].
+        `rotate` = (cos, sin, positions): the xs - K trailing columns of each head of x, rotated by the row's position
+        (first 2 * cos.shape[1] of them, pair (i, i + cos.shape[1])), go to out[t, h * os + N:].
+        `gate` = (g, col): out *= sigmoid(g[t, col + h * os + n])."""
+        T = x.shape[0]
+        H, N, K = w.shape
+        xs, os_ = x.shape[1] // H, out.shape[1] // H
+        rot = xs - K if rotate is not None else 0
+        if xs * H != x.shape[1] or os_ * H != out.shape[1] or out.shape[0] != T or os_ != N + rot or xs < K:
+            raise KernelError(f"head_linear: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not fit")
+        cos, sin, positions = rotate if rotate is not None else (None, None, None)
+        g, col = gate if gate is not None else (None, 0)
+        if g is not None and (g.shape[0] != T or col + H * os_ > g.shape[1] or g.dtype != x.dtype):
+            raise KernelError("head_linear: the gate does not fit")
+        self._count("head_linear")
+        _check(self._latent.kvb_head_linear(
+            _dtype_code(x.dtype), _ptr(x), xs, _ptr(w), _ptr(out), os_, T, N, K, H, _ptr(g), 0 if g is None else g.shape[1], col,
+            rot, 0 if cos is None else cos.shape[1], _ptr(cos), _ptr(sin), 0 if cos is None else cos.shape[0], _ptr(positions),
+            _ptr(self.error_word), self._stream()), "head_linear")
+
+    def latent_attention(self, q: torch.Tensor, batch: StepBatch, kv: PagedKVView, out: torch.Tensor, num_heads: int,
+                         value_dim: int, scale: float, workspace=None) -> None:
+        """Causal softmax(scale * q . key) over the rows of a cache entry with one key row per token that all heads
+        share; a row's value is the first `value_dim` numbers of its key.  q [T, H * key_dim], out [T, H * value_dim]."""
+        T = q.shape[0]
+        spec = kv.spec
+        self._count("attention_generic")
+        _check(self._attn_generic.kvb_paged_attention_shared(
+            _dtype_code(q.dtype), _ptr(q), _ptr(kv.k_pages), _ptr(kv.block_table), kv.block_table.shape[1], _ptr(batch.positions),
+            _ptr(batch.row_segment), _ptr(out), T, num_heads, spec.num_kv_heads, spec.head_dim, value_dim, kv.page_size,
+            spec.window or 0, float(scale), _ptr(self.error_word), self._stream()), "latent_attention")
+
+    def route_top(self, logits: torch.Tensor, chosen: torch.Tensor, share: torch.Tensor) -> None:
+        """chosen[t] = the chosen.shape[1] experts with the largest logits[t] (float32), share[t] = softmax over those."""
+        T, E = logits.shape
+        self._count("route_top")
+        _check(self._moe.kvb_route_top(_ptr(logits), _ptr(chosen), _ptr(share), T, E, chosen.shape[1], self._stream()), "route_top")
+
+    ROUTED_SMALL_PAIRS = 256      # up to this many (row, choice) pairs the grouped products use tiles of 16 rows, else of 64
+
+    def routed_experts(self, x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor,
+                       share: torch.Tensor, out: torch.Tensor, activation: str, workspace) -> None:
+        """out[t] = sum_s share[t, s] * w_down[e] . act(w_up[e] . x[t]), e = chosen[t, s]; w_up [E, F, H], w_down [E, H, F]."""
+        if activation != "relu2":
+            raise KernelError(f"routed_experts: activation '{activation}' is not built")
+        T, H = x.shape
+        E, F, _ = w_up.shape
+        top = chosen.shape[1]
+        pairs = T * top
+        BM = 16 if pairs <= self.ROUTED_SMALL_PAIRS else 64
+        max_tiles = -(-pairs // BM) + E
+        ws, i32 = workspace, torch.int32
+        place = ws.buffer("moe.place", (pairs,), i32)
+        order = ws.buffer("moe.order", (pairs,), i32)
+        plan = ws.buffer("moe.plan", (4,), i32)
+        tiles = ws.buffer("moe.tiles", (max_tiles * 3,), i32)
+        act = ws.buffer("moe.act", (pairs, F), x.dtype)
+        y = ws.buffer("moe.y", (pairs, H), x.dtype)
+        code, stream = _dtype_code(x.dtype), self._stream()
+        self._count("routed_plan")
+        _check(self._moe.kvb_routed_plan(_ptr(chosen), pairs, E, BM, _ptr(place), _ptr(order), _ptr(plan), _ptr(tiles), stream),
+               "routed_plan")
+        self._count("grouped_gemm")
+        _check(self._moe.kvb_grouped_gemm(code, _ptr(x), _ptr(order), top, _ptr(w_up), _ptr(act), _ptr(plan), _ptr(tiles),
+                                          max_tiles, BM, F, H, 1, stream), "grouped_gemm (up)")
+        self._count("grouped_gemm")
+        _check(self._moe.kvb_grouped_gemm(code, _ptr(act), _ptr(order), 0, _ptr(w_down), _ptr(y), _ptr(plan), _ptr(tiles),
+                                          max_tiles, BM, H, F, 0, stream), "grouped_gemm (down)")
+        self._count("routed_combine")
+        _check(self._moe.kvb_routed_combine(code, _ptr(y), _ptr(place), _ptr(share), _ptr(out), T, top, H, stream), "routed_combine")
 
     def sample(self, logits: torch.Tensor, temperature: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor,
                out: torch.Tensor, scratch_val: torch.Tensor, scratch_idx: torch.Tensor) -> None:

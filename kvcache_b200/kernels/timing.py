@@ -46,7 +46,8 @@ def _attention_bytes(batch, kv, num_heads: int) -> int:
 
 class KernelTiming:
     OPERATORS = ("embed", "add_rmsnorm", "silu_mul", "gate_up_act", "linear", "qkv_rope_append", "rope_append_attention",
-                 "paged_attention", "sample")
+                 "paged_attention", "sample", "norm_add_rmsnorm", "latent_norm_rope_append", "head_linear", "latent_attention",
+                 "route_top", "routed_experts")
 
     def __init__(self, kernels, hold_ms: float = 4.0):
         self.kernels = kernels
@@ -83,6 +84,27 @@ class KernelTiming:
             return name, _attention_bytes(batch, kv, num_heads)
         if name == "sample":
             return name, _numel_bytes(args[0])
+        if name == "norm_add_rmsnorm":
+            h, delta, out, tail = args[0], args[1], args[6], (args[8] if len(args) > 8 else kwargs.get("tail"))
+            return name, _numel_bytes(delta) + (2 * _numel_bytes(h) if delta is not None else _numel_bytes(h)) + _numel_bytes(out) + _numel_bytes(tail)
+        if name == "latent_norm_rope_append":
+            proj, q_rank, kv_rank, rot_dim = args[0], args[1], args[2], args[3]
+            return name, proj.shape[0] * (2 * q_rank + 2 * (kv_rank + rot_dim)) * proj.element_size()
+        if name == "head_linear":
+            x, w, out = args[0], args[1], args[2]
+            return f"head_linear {w.shape[0]}x{w.shape[1]}x{w.shape[2]}", _numel_bytes(w) + _numel_bytes(x) + _numel_bytes(out)
+        if name == "latent_attention":
+            q, batch, kv, out = args[0], args[1], args[2], args[3]
+            host = batch.host
+            keys = int((host["starts"] + host["counts"]).sum()) if "starts" in host else batch.max_kv_len * batch.num_segments
+            return name, keys * kv.spec.head_dim * kv.k_pages.element_size() + _numel_bytes(q) + _numel_bytes(out)
+        if name == "route_top":
+            return name, _numel_bytes(args[0])
+        if name == "routed_experts":
+            x, w_up, w_down, chosen, out = args[0], args[1], args[2], args[3], args[5]
+            used = min(w_up.shape[0], chosen.numel())          # experts a step can touch at most
+            per_expert = (w_up[0].numel() + w_down[0].numel()) * w_up.element_size()
+            return f"routed_experts {w_up.shape[0]}x{w_up.shape[1]}x{w_up.shape[2]}", used * per_expert + _numel_bytes(x) + _numel_bytes(out)
         return name, 0
 
     # ---- switching on and off -------------------------------------------------------------------------
