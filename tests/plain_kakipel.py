@@ -160,3 +160,13 @@ def residual_streams(config: dict, w: Dict[str, torch.Tensor], tokens: Sequence[
 def logits_of(config: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int]) -> torch.Tensor:
     x = residual_streams(config, w, tokens)[-1]
     return linear(rms_norm(x, w["final.norm"], float(config["norm"]["eps"])), w["head"])
+
+
+def greedy_generate(config: dict, w: Dict[str, torch.Tensor], prompt: Sequence[int], new_tokens: int) -> List[int]:
+    """Recomputes the whole sequence for every new token."""
+    tokens, out = list(prompt), []
+    for _ in range(new_tokens):
+        nxt = int(torch.argmax(logits_of(config, w, tokens)[-1]))
+        tokens.append(nxt)
+        out.append(nxt)
+    return out
