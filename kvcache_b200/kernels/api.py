@@ -18,6 +18,7 @@ import torch
 from ..parts.base import PagedKVView, StepBatch
 from . import build
 from .attention_plan import PagedAttentionPlanner
+from .latent_plan import LatentAttentionPlanner
 
 _c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 
@@ -110,6 +111,12 @@ _SIGNATURES = {
                                         _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p],
         "kvb_head_linear": [_c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                             _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p],
+    },
+    "latent_flash": {
+        "kvb_latent_flash_supports": [_c_int, _c_int, _c_int],
+        "kvb_latent_flash": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p,
+                             _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
+                             _c_void_p, _c_void_p],
     },
     "moe": {
         "kvb_route_top": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
@@ -220,6 +227,9 @@ class CudaKernels(KernelSet):
         self._gemm_simt = _Library("gemm_simt")
         self._latent = _Library("latent")
         self._moe = _Library("moe")
+        self._latent_flash = _Library("latent_flash")
+        self.latent_flash = True             # bfloat16, key rows in steps of 8 numbers: the tensor-core kernel over shared key rows
+        self._latent_planners: Dict[int, "LatentAttentionPlanner"] = {}
         self._sampling = _Library("sampling")
         self._gemm_skinny = _Library("gemm_skinny")
         self._gemm_tc = _Library("gemm_tcgen05")
@@ -341,6 +351,13 @@ class CudaKernels(KernelSet):
         if self._attention_planner is None:
             self._attention_planner = PagedAttentionPlanner()
         return self._attention_planner
+
+    def latent_attention_planner(self, heads: int) -> LatentAttentionPlanner:
+        """The work list `latent_attention` reads from `StepBatch.plans` for mixers of `heads` heads (one planner for all of them)."""
+        found = self._latent_planners.get(heads)
+        if found is None:
+            found = self._latent_planners[heads] = LatentAttentionPlanner(heads, 2 * self.sm_count)
+        return found
 
     # ---- operators ---------------------------------------------------------
     def embed(self, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, src: Optional[torch.Tensor] = None,
@@ -742,6 +759,21 @@ class CudaKernels(KernelSet):
         share; a row's value is the first `value_dim` numbers of its key.  q [T, H * key_dim], out [T, H * value_dim]."""
         T = q.shape[0]
         spec = kv.spec
+        plan = batch.plans.get(f"latent_attention.h{num_heads}")
+        if (self.latent_flash and q.dtype == torch.bfloat16 and plan is not None and workspace is not None and spec.num_kv_heads == 1
+                and self._latent_flash.kvb_latent_flash_supports(spec.head_dim, value_dim, plan.counts["bm"]) == 0):
+            n, tiles, nsplit, bm = (plan.counts[k] for k in ("items", "tiles", "nsplit", "bm"))
+            part_o = part_ml = None
+            if nsplit > 1:
+                part_o = workspace.buffer("latent.part_o", (n * bm * value_dim,), torch.float32)
+                part_ml = workspace.buffer("latent.part_ml", (n * bm * 2,), torch.float32)
+            self._count("latent_flash")
+            _check(self._latent_flash.kvb_latent_flash(
+                _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.block_table), kv.block_table.shape[1], _ptr(plan.arrays["items"]), n,
+                tiles, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len), _ptr(part_o), _ptr(part_ml),
+                num_heads, spec.head_dim, value_dim, bm, kv.page_size, spec.window or 0, float(scale), nsplit,
+                _ptr(self.error_word), self._stream()), "latent_flash")
+            return
         self._count("attention_generic")
         _check(self._attn_generic.kvb_paged_attention_shared(
             _dtype_code(q.dtype), _ptr(q), _ptr(kv.k_pages), _ptr(kv.block_table), kv.block_table.shape[1], _ptr(batch.positions),

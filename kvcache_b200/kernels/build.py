@@ -32,6 +32,7 @@ MODULES: Dict[str, dict] = {
     "gemm_simt": {"src": "gemm_simt.cu", "deps": ["common.cuh"]},
     "latent": {"src": "latent.cu", "deps": ["common.cuh"]},
     "moe": {"src": "moe.cu", "deps": ["common.cuh"]},
+    "latent_flash": {"src": "latent_flash.cu", "deps": ["common.cuh"]},
     "sampling": {"src": "sampling.cu", "deps": ["common.cuh"]},
     "gemm_skinny": {"src": "gemm_skinny.cu", "deps": ["common.cuh"]},
     "gemm_tcgen05": {"src": "gemm_tcgen05.cu", "deps": ["common.cuh", "tc_common.cuh"]},

@@ -100,6 +100,71 @@ def test_head_linear(kernels, dtype, T, shape):
         assert_close(got, ref, TOL[dtype], form)
 
 
+def _with_latent_plan(batch, segments, heads, blocks_wanted=296):
+    """Adds the work list of the tensor-core kernel over shared key rows to a hand-made batch."""
+    import dataclasses
+    from kvcache_b200.kernels.latent_plan import LatentAttentionPlanner
+    from kvcache_b200.parts.base import StepPlan
+    planner = LatentAttentionPlanner(heads, blocks_wanted)
+    arrays, counts = planner.plan(np.asarray([s for s, _ in segments]), np.asarray([n for _, n in segments]))
+    plans = dict(batch.plans)
+    plans[planner.name] = StepPlan({k: torch.tensor(np.array(v), dtype=torch.int32) for k, v in arrays.items()}, counts)
+    return dataclasses.replace(batch, plans=plans)
+
+
+FLASH_CASES = [dict(H=8, D=96, Dv=64, page=16), dict(H=3, D=40, Dv=24, page=8), dict(H=16, D=576, Dv=512, page=32),
+               dict(H=5, D=88, Dv=72, page=16), dict(H=20, D=160, Dv=128, page=64), dict(H=1, D=72, Dv=56, page=16),
+               dict(H=4, D=320, Dv=256, page=16)]
+FLASH_SEGMENTS = {"decode": [(70, 1), (129, 1), (0, 1), (1000, 1)], "prompt": [(0, 333)], "portion": [(190, 67), (15, 2)],
+                  "mixed": [(0, 33), (70, 1), (15, 2), (129, 1), (300, 130)]}
+
+
+@pytest.mark.parametrize("wanted", [296, 4])
+@pytest.mark.parametrize("kind", list(FLASH_SEGMENTS))
+@pytest.mark.parametrize("case", FLASH_CASES)
+def test_latent_attention_tensor_cores(kernels, case, kind, wanted):
+    """The bfloat16 tensor-core kernel (tiles of (token, head) rows, splits over the keys added by a second kernel)
+    against the plain statement, with and without splits."""
+    H, D, Dv, page = case["H"], case["D"], case["Dv"], case["page"]
+    segments = FLASH_SEGMENTS[kind]
+    dtype = torch.bfloat16
+    batch, kv = paged_scenario(segments, num_kv_heads=1, head_dim=D, page_size=page, dtype=dtype, device="cpu", seed=5)
+    batch = _with_latent_plan(batch, segments, H, wanted)
+    T = batch.num_tokens
+    q = _rand(T, H * D, dtype=dtype, seed=6)
+    ref, got = torch.zeros(T, H * Dv, dtype=dtype), torch.full((T, H * Dv), 7.0, dtype=dtype, device=DEV)
+    TorchKernels(wide=True).latent_attention(q, batch, kv, ref, H, Dv, D ** -0.5)
+    from kvcache_b200.engine.workspace import Workspace
+    before = kernels.launch_counts["latent_flash"]
+    kernels.latent_attention(q.to(DEV), batch_to(batch, DEV), clone_kv(kv, DEV), got, H, Dv, D ** -0.5, Workspace(DEV))
+    kernels.check_errors()
+    assert kernels.launch_counts["latent_flash"] == before + 1
+    assert_close(got, ref, TOL[dtype])
+
+
+def test_latent_attention_tensor_cores_one_far_key(kernels):
+    """One key takes all the weight of one (token, head) row: at a page border, in another split, in a prompt's portion."""
+    H, D, Dv, page = 6, 96, 64, 16
+    segments = [(900, 1), (0, 200)]
+    dtype = torch.bfloat16
+    batch, kv = paged_scenario(segments, num_kv_heads=1, head_dim=D, page_size=page, dtype=dtype, device="cpu", seed=9)
+    batch = _with_latent_plan(batch, segments, H)
+    q = _rand(batch.num_tokens, H * D, dtype=dtype, seed=10, scale=0.02)
+    probes = [(0, 0, 2, 15), (0, 0, 3, 16), (0, 0, 5, 640), (1, 150, 1, 63), (1, 199, 4, 64), (1, 77, 0, 77)]   # segment, token, head, key
+    for seg, tok, head, key in probes:
+        row = tok if seg == 1 else 0
+        row += 1 if seg == 1 else 0
+        k = kv.k_pages[int(kv.block_table[seg, key // page]), 0, key % page].float()
+        q.view(-1, H, D)[row, head] = (k * 3.0).to(dtype)
+    got = torch.zeros(batch.num_tokens, H * Dv, dtype=dtype, device=DEV)
+    from kvcache_b200.engine.workspace import Workspace
+    kernels.latent_attention(q.to(DEV), batch_to(batch, DEV), clone_kv(kv, DEV), got, H, Dv, 1.0, Workspace(DEV))
+    for seg, tok, head, key in probes:
+        row = tok + 1 if seg == 1 else 0
+        k = kv.k_pages[int(kv.block_table[seg, key // page]), 0, key % page]
+        assert_close(got.view(-1, H, Dv)[row, head], k[:Dv], 2e-2, f"segment {seg} token {tok} key {key}")
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("case", [dict(H=8, D=96, Dv=64, page=16), dict(H=3, D=40, Dv=24, page=8), dict(H=16, D=576, Dv=512, page=32)])
 def test_latent_attention(kernels, dtype, case):
