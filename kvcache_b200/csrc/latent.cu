@@ -8,6 +8,7 @@
 // Everything between loads and stores is float32: sums of squares, norms, angles, the gate.  Reductions run in a
 // fixed order per row (`block_sum`), so a row's result does not depend on the rows beside it.
 #include "common.cuh"
+#include "mma_tile.cuh"
 
 // ---------------------------------------------------------------------------------------------------------------
 // One block per output row.  v = h[r] + (dw ? d * rsqrt(mean(d^2) + deps) * dw : d); rows == null: h[r] = v.
@@ -253,6 +254,57 @@ __global__ void __launch_bounds__(256) head_linear_simt_kernel(const T* __restri
     }
 }
 
+// The same on the tensor cores (bfloat16; K, xs and the heads' offsets in steps of 8 elements, os even).
+template <int MT>
+__global__ void __launch_bounds__(mt::THREADS) head_linear_mma_kernel(const bf16* __restrict__ x, int xs, const bf16* __restrict__ w,
+                                                                      bf16* __restrict__ out, int os, int M, int N, int K, int H,
+                                                                      const bf16* __restrict__ gate, int gs, int gc, int rot,
+                                                                      int rot_half, const float* __restrict__ cos_t,
+                                                                      const float* __restrict__ sin_t, int table_len,
+                                                                      const int* __restrict__ positions, int* __restrict__ err) {
+    pdl_wait();
+    pdl_launch_dependents();
+    constexpr int BM = 16 * MT;
+    __shared__ __align__(16) mt::Smem<MT> sm;
+    const int h = blockIdx.z, m0 = blockIdx.y * BM, n0 = blockIdx.x * mt::BN;
+    const size_t xrow = (size_t)H * xs, orow = (size_t)H * os;
+    const bf16* xh = x + (size_t)h * xs;
+    auto a_row = [&](int r) -> const bf16* { return m0 + r < M ? xh + (size_t)(m0 + r) * xrow : nullptr; };
+    auto store = [&](int r, int c, float v0, float v1) {
+        const int gm = m0 + r, gn = n0 + c;
+        if (gm >= M || gn >= N) return;
+        bf16* dst = out + (size_t)gm * orow + (size_t)h * os + gn;
+        if (gate) {
+            const bf16* gp = gate + (size_t)gm * gs + gc + (size_t)h * os + gn;
+            v0 *= 1.f / (1.f + expf(-__bfloat162float(gp[0])));
+            if (gn + 1 < N) v1 *= 1.f / (1.f + expf(-__bfloat162float(gp[1])));
+        }
+        if (gn + 1 < N) *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(v0, v1);
+        else dst[0] = __float2bfloat16_rn(v0);
+    };
+    mt::tile_product<MT>(sm, a_row, w + ((size_t)h * N + n0) * K, min(mt::BN, N - n0), K, store);
+    if (rot > 0 && blockIdx.x == 0) {
+        for (int e = threadIdx.x; e < BM * rot; e += mt::THREADS) {
+            const int row = e / rot, i = e % rot;
+            const int gm = m0 + row;
+            if (gm >= M) continue;
+            const int pos = positions[gm];
+            const bool pos_ok = pos >= 0 && pos < table_len;
+            if (!pos_ok) atomicOr(err, KVB_DEV_BAD_POS);
+            const bf16* src = xh + (size_t)gm * xrow + K;
+            float v = __bfloat162float(src[i]);
+            if (i < 2 * rot_half && pos_ok) {
+                const bool low = i < rot_half;
+                const int t = low ? i : i - rot_half;
+                const float vp = __bfloat162float(src[low ? i + rot_half : i - rot_half]);
+                const float c = cos_t[(size_t)pos * rot_half + t], s = sin_t[(size_t)pos * rot_half + t];
+                v = low ? (v * c - vp * s) : (v * c + vp * s);
+            }
+            out[(size_t)gm * orow + (size_t)h * os + N + i] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
 template <typename T, int BM>
 static void launch_head_linear(const T* x, int xs, const T* w, T* out, int os, int M, int N, int K, int H, const T* gate, int gs,
                                int gc, int rot, int rot_half, const float* cos_t, const float* sin_t, int table_len,
@@ -274,7 +326,21 @@ KVB_API int kvb_head_linear(int dtype, const void* x, int xs, const void* w, voi
     if (dtype == KVB_F32) {
         if (M <= 16) KVB_HEAD_LINEAR(float, 16); else KVB_HEAD_LINEAR(float, 64);
     } else if (dtype == KVB_BF16) {
-        if (M <= 16) KVB_HEAD_LINEAR(bf16, 16); else KVB_HEAD_LINEAR(bf16, 64);
+        const bool aligned = K % 8 == 0 && xs % 8 == 0 && os % 2 == 0 && ((uintptr_t)x | (uintptr_t)w) % 16 == 0 &&
+                             (uintptr_t)out % 4 == 0;
+        if (aligned && getenv("KVB_HEAD_LINEAR_SIMT") == nullptr) {
+            const bf16 *xb = (const bf16*)x, *wb = (const bf16*)w, *gb = (const bf16*)gate;
+            if (M <= 16)
+                kvb_launch(head_linear_mma_kernel<1>, dim3((N + 63) / 64, (M + 15) / 16, H), dim3(mt::THREADS), 0, stream, xb, xs, wb,
+                           (bf16*)out, os, M, N, K, H, gb, gs, gc, rot, rot_half, cos_t, sin_t, table_len, positions, err);
+            else
+                kvb_launch(head_linear_mma_kernel<4>, dim3((N + 63) / 64, (M + 63) / 64, H), dim3(mt::THREADS), 0, stream, xb, xs, wb,
+                           (bf16*)out, os, M, N, K, H, gb, gs, gc, rot, rot_half, cos_t, sin_t, table_len, positions, err);
+        } else if (M <= 16) {
+            KVB_HEAD_LINEAR(bf16, 16);
+        } else {
+            KVB_HEAD_LINEAR(bf16, 64);
+        }
     } else {
         return KVB_ERR_DTYPE;
     }

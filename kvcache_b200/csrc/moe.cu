@@ -10,6 +10,7 @@
 // tiles that the plan made return at once.  A pair's result does not depend on where it sits in its tile, so the
 // (unordered) placement by atomic counters leaves every row's result what it would be alone.
 #include "common.cuh"
+#include "mma_tile.cuh"
 
 #define MOE_MAX_EXPERTS 1024
 
@@ -190,6 +191,38 @@ __global__ void __launch_bounds__(256) grouped_gemm_simt_kernel(const T* __restr
     }
 }
 
+// The same on the tensor cores (bfloat16, K a multiple of 8, N even).
+template <int MT, int ACT>
+__global__ void __launch_bounds__(mt::THREADS) grouped_gemm_mma_kernel(const bf16* __restrict__ a, const int* __restrict__ sorted_pair,
+                                                                       int gather_div, const bf16* __restrict__ w,
+                                                                       bf16* __restrict__ out, const int* __restrict__ plan,
+                                                                       const int* __restrict__ tiles, int N, int K) {
+    pdl_wait();
+    pdl_launch_dependents();
+    if ((int)blockIdx.y >= plan[0]) return;
+    constexpr int BM = 16 * MT;
+    __shared__ __align__(16) mt::Smem<MT> sm;
+    __shared__ int src_row[BM];
+    const int expert = tiles[3 * blockIdx.y], row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+    const int n0 = blockIdx.x * mt::BN;
+    for (int i = threadIdx.x; i < BM; i += mt::THREADS)
+        src_row[i] = i < rows ? (gather_div > 0 ? sorted_pair[row0 + i] / gather_div : row0 + i) : -1;
+    __syncthreads();
+    auto a_row = [&](int r) -> const bf16* { return src_row[r] >= 0 ? a + (size_t)src_row[r] * K : nullptr; };
+    auto store = [&](int r, int c, float v0, float v1) {
+        const int gn = n0 + c;
+        if (r >= rows || gn >= N) return;
+        if (ACT == 1) {
+            v0 = fmaxf(v0, 0.f); v0 *= v0;
+            v1 = fmaxf(v1, 0.f); v1 *= v1;
+        }
+        bf16* dst = out + (size_t)(row0 + r) * N + gn;
+        if (gn + 1 < N) *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(v0, v1);
+        else dst[0] = __float2bfloat16_rn(v0);
+    };
+    mt::tile_product<MT>(sm, a_row, w + ((size_t)expert * N + n0) * K, min(mt::BN, N - n0), K, store);
+}
+
 template <typename T, int BM>
 static void launch_grouped(const T* a, const int* sorted_pair, int gather_div, const T* w, T* out, const int* plan,
                            const int* tiles, int max_tiles, int N, int K, int act, cudaStream_t stream) {
@@ -212,7 +245,20 @@ KVB_API int kvb_grouped_gemm(int dtype, const void* a, const int* sorted_pair, i
     if (dtype == KVB_F32) {
         if (BM == 16) KVB_GROUPED(float, 16); else KVB_GROUPED(float, 64);
     } else if (dtype == KVB_BF16) {
-        if (BM == 16) KVB_GROUPED(bf16, 16); else KVB_GROUPED(bf16, 64);
+        const bool aligned = K % 8 == 0 && N % 2 == 0 && ((uintptr_t)a | (uintptr_t)w) % 16 == 0 && (uintptr_t)out % 4 == 0;
+        if (aligned && getenv("KVB_GROUPED_SIMT") == nullptr) {
+            dim3 grid((N + 63) / 64, max_tiles);
+            const bf16 *ab = (const bf16*)a, *wb = (const bf16*)w;
+#define KVB_GROUPED_MMA(MT, ACT_) \
+    kvb_launch(grouped_gemm_mma_kernel<MT, ACT_>, grid, dim3(mt::THREADS), 0, stream, ab, sorted_pair, gather_div, wb, (bf16*)out, plan, tiles, N, K)
+            if (BM == 16) { if (act == 1) KVB_GROUPED_MMA(1, 1); else KVB_GROUPED_MMA(1, 0); }
+            else { if (act == 1) KVB_GROUPED_MMA(4, 1); else KVB_GROUPED_MMA(4, 0); }
+#undef KVB_GROUPED_MMA
+        } else if (BM == 16) {
+            KVB_GROUPED(bf16, 16);
+        } else {
+            KVB_GROUPED(bf16, 64);
+        }
     } else {
         return KVB_ERR_DTYPE;
     }

@@ -30,8 +30,8 @@ MODULES: Dict[str, dict] = {
     "rope_append": {"src": "rope_append.cu", "deps": ["common.cuh"]},
     "attention_generic": {"src": "attention_generic.cu", "deps": ["common.cuh"]},
     "gemm_simt": {"src": "gemm_simt.cu", "deps": ["common.cuh"]},
-    "latent": {"src": "latent.cu", "deps": ["common.cuh"]},
-    "moe": {"src": "moe.cu", "deps": ["common.cuh"]},
+    "latent": {"src": "latent.cu", "deps": ["common.cuh", "mma_tile.cuh"]},
+    "moe": {"src": "moe.cu", "deps": ["common.cuh", "mma_tile.cuh"]},
     "latent_flash": {"src": "latent_flash.cu", "deps": ["common.cuh"]},
     "sampling": {"src": "sampling.cu", "deps": ["common.cuh"]},
     "gemm_skinny": {"src": "gemm_skinny.cu", "deps": ["common.cuh"]},

@@ -74,15 +74,21 @@ def config_dict(name: str, **changes) -> dict:
     return out
 
 
-def make_kakipel_folder(tmp_path, name: str, seed: int = 0, dtype=torch.float32, sharpen: float = 1.0, std: float = 0.08) -> str:
+def make_kakipel_folder(tmp_path, name: str, seed: int = 0, dtype=torch.float32, sharpen: float = 1.0, std: float = 0.08,
+                        all_experts: bool = False) -> str:
     """A random-weights folder for configuration `name`.  `sharpen` multiplies every mixer's score scale, so that the
-    softmax picks out single keys and a wrong or missing key shows in the logits."""
+    softmax picks out single keys and a wrong or missing key shows in the logits.  `all_experts`: every routed layer
+    chooses all its experts - for comparisons in bfloat16, where rounding may turn a close call between two experts the
+    other way than the plain implementation's float64 does, which changes a position's logits by far more than rounding
+    (the choice itself is held to the plain implementation in float32 and at kernel level)."""
     import kvcache_b200  # registers the architectures  # noqa: F401
     from kvcache_b200.config import config_from_dict
     from kvcache_b200.weights import write_random_model
     data = config_dict(name, initializer_range=std)
     for layer in data["layers"]:
         layer["mixer"]["scale"] *= sharpen
-    folder = os.path.join(str(tmp_path), f"kaki_{name}_{seed}_{sharpen}")
+        if all_experts and layer["mlp"] is not None and layer["mlp"]["kind"] == "moe":
+            layer["mlp"]["router"]["top"] = layer["mlp"]["router"]["experts"]
+    folder = os.path.join(str(tmp_path), f"kaki_{name}_{seed}_{sharpen}_{int(all_experts)}")
     write_random_model(folder, config_from_dict(data), seed, dtype)
     return folder

@@ -27,7 +27,7 @@ def kernels():
 
 
 def _runner(tmp_path, kernels, name, dtype, num_pages=64, sharpen=1.0, **kw):
-    folder = make_kakipel_folder(tmp_path, name, sharpen=sharpen, dtype=torch.bfloat16)
+    folder = make_kakipel_folder(tmp_path, name, sharpen=sharpen, dtype=torch.bfloat16, all_experts=dtype == "bfloat16")
     runner = make_runner(folder, kernels, dtype=dtype, device=DEV, page_size=PAGE_SIZE[name], num_pages=num_pages, **kw)
     config, weights = plain.read_folder(folder)
     return runner, config, weights
@@ -123,7 +123,7 @@ def test_long_decoding_under_graphs_matches_eager_and_plain(tmp_path, kernels, d
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_through_the_entry_point(tmp_path, kernels, dtype):
     from kvcache_b200 import LLM, SamplingParams
-    folder = make_kakipel_folder(tmp_path, "Q", dtype=torch.bfloat16)
+    folder = make_kakipel_folder(tmp_path, "Q", dtype=torch.bfloat16, all_experts=dtype == "bfloat16")
     config, weights = plain.read_folder(folder)
     prompts = [random_tokens(config["vocab"], n, 40 + n) for n in (1, 9, 24, 40, 63)]
     llm = LLM(folder, kernels=kernels, dtype=dtype, device=DEV, page_size=16, num_pages=40, max_running=3, max_tokens_per_step=48,
@@ -143,7 +143,7 @@ def test_greedy_generation_through_the_entry_point(tmp_path, kernels, dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_replay_program(tmp_path, dtype):
     """bin/trace_run as a user runs it, on a Kakipel folder: mixed steps, requests that pause, pages used again."""
-    folder = make_kakipel_folder(tmp_path, "P", dtype=torch.bfloat16)
+    folder = make_kakipel_folder(tmp_path, "P", dtype=torch.bfloat16, all_experts=dtype == "bfloat16")
     config, weights = plain.read_folder(folder)
     seqs = {k: random_tokens(config["vocab"], n, 20 + i) for i, (k, n) in enumerate([("a", 70), ("b", 33), ("c", 64), ("d", 50)])}
     plan = [([("a", 40), ("b", 2)], []), ([("b", 1), ("c", 64)], ["c"]), ([("a", 1), ("b", 30)], ["b"]), ([("d", 50), ("a", 29)], ["a", "d"])]
