@@ -66,18 +66,18 @@ def test_float32_rows_do_not_depend_on_the_batch_or_the_cut(tmp_path, kernels, n
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_sharp_attention_over_many_pages(tmp_path, kernels, dtype):
     """Sharpened scores make single far keys carry the softmax: keys at page borders, in a portion's first rows and far
-    behind a decoded token all have to be found.  bfloat16 is held to what its own rounding of sharp scores allows."""
-    runner, config, weights = _runner(tmp_path, kernels, "P", dtype, sharpen=40.0, num_pages=96, max_tokens_per_step=640,
+    behind a decoded token all have to be found.  Sharp scores magnify rounding too: bfloat16, whose rounding of a score
+    40 times larger would itself change which key wins, is sharpened less and held to less (single far keys in bfloat16
+    are met at kernel level, where one key takes all the weight by construction)."""
+    sharpen, rel = (40.0, 2e-3) if dtype == "float32" else (5.0, 0.08)
+    runner, config, weights = _runner(tmp_path, kernels, "P", dtype, sharpen=sharpen, num_pages=96, max_tokens_per_step=640,
                                       max_tokens_per_request=640)
     tokens = random_tokens(config["vocab"], 600, 5)
     want = plain.logits_of(config, weights, tokens)
-    rel = 2e-3 if dtype == "float32" else 0.25
     got = replay_modes.portions(runner, tokens, [7, 2, 57, 64, 3, 259, 8, 168, 32])
     assert_close(got, want, rel)
     got = replay_modes.last_32_one_by_one(runner, tokens)
     assert_close(got, want[-33:], rel)
-    if dtype == "bfloat16":      # the typical position is far closer than the worst one
-        assert ((got.double().cpu() - want[-33:]).abs().mean() / want.abs().max()).item() < 0.03
 
 
 def test_one_far_key_carries_a_decoded_token(tmp_path, kernels):
