@@ -413,6 +413,158 @@ def run_ours(args) -> int:
     return 0
 
 
+# ---- --design: another architecture of the engine beside the Qwen2 shape of equal size -----------------------------------------
+def _kakipel_mixer(heads, dim, rot_dim, vdim, kv_rank, q_rank):
+    return {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank,
+            "scale": (dim + rot_dim) ** -0.5,
+            "rot": {"base": 10000.0, "dims": rot_dim, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+
+
+def design_sizes():
+    """Layer sizes that resemble real models, as (name, Kakipel config, Qwen2 config of equal width, layer runs, feed-forward
+    width and vocabulary).  Both have four layer runs; the Kakipel models run a dense and a routed layer twice (a looped
+    pair), the routed layer with as many active feed-forward weights per token as the dense one."""
+    out = []
+    for name, width, heads, dim, rot, vdim, kv_rank, q_rank, ff, experts, top, kv_heads, vocab in (
+            ("0.5B-like", 896, 14, 64, 32, 64, 256, 384, 4864, 16, 2, 2, 32768),
+            ("3B-like", 2048, 16, 128, 64, 128, 512, 768, 11008, 32, 4, 2, 32768)):
+        mixer = _kakipel_mixer(heads, dim, rot, vdim, kv_rank, q_rank)
+        layers = [{"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}},
+                  {"type": "latent_attention", "mixer": mixer,
+                   "mlp": {"kind": "moe", "expert": {"ff": 3 * ff // (2 * top) // 64 * 64}, "router": {"experts": experts, "top": top}}}]
+        kaki = {"architecture": "Kakipel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": layers,
+                "loop": {"start": 0, "stop": 2, "times": 2}, "initializer_range": 0.02}
+        qwen = dict(QWEN25_05B, hidden_size=width, num_hidden_layers=4, max_window_layers=4, num_attention_heads=heads,
+                    num_key_value_heads=kv_heads, head_dim=dim, intermediate_size=ff, vocab_size=vocab, tie_word_embeddings=False)
+        out.append((name, kaki, qwen))
+    return out
+
+
+def _write_design_folder(tmp, tag, config):
+    import torch
+    import kvcache_b200  # noqa: F401
+    from kvcache_b200.config import config_from_dict
+    from kvcache_b200.weights import write_random_model
+    return write_random_model(os.path.join(tmp, tag), config_from_dict(config), seed=0, dtype=torch.bfloat16)
+
+
+def _time_prefill_plain(folder, tokens, clocks, name, repeats=3, warm=5):
+    """A prompt of `tokens` tokens in one step (replayed from a graph once its shape has come a few times): milliseconds."""
+    import torch
+    from kvcache_b200.config.options import EngineOptions
+    from kvcache_b200.engine.core import EngineCore
+    from kvcache_b200.engine.runner import StepEntry
+    core = EngineCore(folder, EngineOptions(dtype="bfloat16", page_size=16, max_cached_tokens=tokens + 16, max_running=1,
+                                            max_tokens_per_step=tokens, max_model_len=tokens + 16, use_graphs=True))
+    ids = torch.randint(0, core.model.vocab_size, (tokens,), generator=torch.Generator().manual_seed(3)).to(torch.int32).numpy()
+    times = []
+    with clocks.region(name):
+        for i in range(warm + repeats):
+            slot = core.cache.admit()
+            torch.cuda.synchronize()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            core.runner.step([StepEntry(slot, ids, [tokens - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            core.cache.release(slot)
+            if i >= warm:
+                times.append(begin.elapsed_time(end))
+    core.kernels.check_errors()
+    del core
+    torch.cuda.empty_cache()
+    return statistics.median(times)
+
+
+def _classes(report, repeats, peaks):
+    """Per class of kernel: microseconds, what it has to move and to compute, and how far it is from the slower of the two
+    bounds (bytes over the measured copy bandwidth, flops over the measured bfloat16 product)."""
+    out = {}
+    for name, entry in sorted(report.items(), key=lambda kv: -kv[1]["us"]):
+        us = entry["us"] / repeats
+        nbytes, flops = entry["bytes"] / repeats, entry["flops"] / repeats
+        bound_us = max(nbytes / (peaks["hbm_gbs"] * 1e9), flops / (peaks["bf16_tflops"] * 1e12)) * 1e6
+        item = {"us": round(us, 1), "calls": entry["calls"] // repeats, "launches": entry["launches"] // repeats}
+        if nbytes:
+            item["gbs"] = round(nbytes / (us * 1e-6) / 1e9, 1)
+        if flops:
+            item["tflops"] = round(flops / (us * 1e-6) / 1e12, 1)
+        if bound_us > 0:
+            item["roofline_frac"] = round(bound_us / us, 3)
+            item["bound"] = "flops" if flops / (peaks["bf16_tflops"] * 1e12) > nbytes / (peaks["hbm_gbs"] * 1e9) else "bytes"
+        out[name] = item
+    return out
+
+
+def _time_classes(folder, peaks, mode, batch, context, tokens, repeats=3):
+    """One step launched kernel by kernel with CUDA events around every operator (`mode`: "decode" - `batch` requests of
+    `context` cached tokens - or "prefill" - one prompt of `tokens`)."""
+    import torch
+    from kvcache_b200.config.options import EngineOptions
+    from kvcache_b200.engine.core import EngineCore
+    from kvcache_b200.engine.runner import StepEntry
+    if mode == "decode":
+        core = _decode_engine(folder, batch, context, use_graphs=False)
+        slots = [core.cache.admit() for _ in range(batch)]
+        fill_cache_randomly(core, slots, context - repeats - 4)
+        step = lambda: core.runner.step([StepEntry(s, (1,), (0,), (0.0, i, 0)) for i, s in enumerate(slots)], sample=True)
+    else:
+        core = EngineCore(folder, EngineOptions(dtype="bfloat16", page_size=16, max_cached_tokens=tokens + 16, max_running=1,
+                                                max_tokens_per_step=tokens, max_model_len=tokens + 16, use_graphs=False))
+        ids = torch.randint(0, core.model.vocab_size, (tokens,), generator=torch.Generator().manual_seed(3)).to(torch.int32).numpy()
+
+        def step():
+            slot = core.cache.admit()
+            core.runner.step([StepEntry(slot, ids, [tokens - 1])])
+            torch.cuda.synchronize()
+            core.cache.release(slot)
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    core.kernels.start_timing(hold_ms=20.0)
+    for _ in range(repeats):
+        step()
+    report = core.kernels.stop_timing()
+    core.kernels.check_errors()
+    del core
+    torch.cuda.empty_cache()
+    return _classes(report, repeats, peaks)
+
+
+def run_design(args) -> int:
+    """`--design kakipel`: decode and prefill throughput of the Kakipel architecture at sizes that resemble real models'
+    layers, beside the Qwen2 architecture at equal width, layer runs, feed-forward width and vocabulary (random weights,
+    random cache contents for decode), and every class of kernel of one step of each against its roofline."""
+    peaks = load_peaks()
+    clocks = ClockSampler().start()
+    results = []
+    with tempfile.TemporaryDirectory() as tmp:
+        for name, kaki, qwen in design_sizes():
+            if args.sizes and name not in args.sizes.split(","):
+                continue
+            entry = {"size": name, "width": kaki["width"], "layer_runs": 4, "vocab": kaki["vocab"]}
+            for arch, config in (("kakipel", kaki), ("qwen2", qwen)):
+                folder = _write_design_folder(tmp, f"{arch}_{name}", config)
+                run = time_decode(folder, args.batch, args.context, args.steps, args.warmup, clocks, f"{arch} {name} decode")
+                prefill_ms = _time_prefill_plain(folder, PREFILL_TOKENS, clocks, f"{arch} {name} prefill")
+                item = {"decode_tok_s": round(run["tok_s"], 1), "decode_ms_per_step": round(run["ms_per_step"], 4),
+                        "decode_gbs": round(run["bytes_per_step"] / (run["ms_per_step"] / 1e3) / 1e9, 1),
+                        "decode_frac_of_copy_peak": round(run["bytes_per_step"] / (run["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"], 4),
+                        "prefill_tok_s": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+                        "gpu_launches_per_decode_step": run["launches"] // args.steps}
+                if not args.skip_kernels:
+                    item["decode_kernels"] = _time_classes(folder, peaks, "decode", args.batch, args.context, PREFILL_TOKENS)
+                    item["prefill_kernels"] = _time_classes(folder, peaks, "prefill", args.batch, args.context, PREFILL_TOKENS)
+                entry[arch] = item
+            results.append(entry)
+    clocks.stop()
+    print(json.dumps({"metric": f"decode tok/s at batch {args.batch}, context {args.context}, and prefill tok/s of one {PREFILL_TOKENS}-token prompt: "
+                                "Kakipel beside Qwen2 at equal sizes", "impl": "ours", "design": "kakipel", "dtype": "bf16",
+                      "data": "synthetic", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "peaks": peaks, "sizes": results,
+                      "clocks": {"how": clocks.how, "regions": clocks.regions}}))
+    return 0
+
+
 def run_reference(args) -> int:
     """The same workload through the unmodified reference.  Its `qwen_serve` prints no timing, so the decode
     time is the difference between two runs of the same eight requests that differ only in the number of new
@@ -500,6 +652,9 @@ def main() -> int:
     parser.add_argument("--skip-prefill", action="store_true")
     parser.add_argument("--skip-kernels", action="store_true")
     parser.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for profilers)")
+    parser.add_argument("--design", default=None, choices=["kakipel"],
+                        help="instead of the default workload: this architecture beside Qwen2 at equal sizes (decode, prefill, kernels)")
+    parser.add_argument("--sizes", default="", help="with --design: the sizes to run, with commas between them (default: all)")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -508,6 +663,8 @@ def main() -> int:
         print(f"bench.py measures a one-GPU engine: --gpus {args.gpus} is not supported (this build has no multi-GPU path)")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.design:
+        return run_design(args)
     return run_ours(args)
 
 

@@ -69,7 +69,8 @@ KVB_API int kvb_route_top(const float* logits, int* chosen, float* share, int T,
 }
 
 // One block.  plan = [tile count | expert offsets (E + 1) | cursors (E)]; tiles[i] = (expert, first sorted row, rows).
-__global__ void routed_plan_kernel(const int* __restrict__ chosen, int pairs, int E, int BM, int* __restrict__ place,
+// `pad_runs`: every expert's run of rows starts at a multiple of BM (the rows between the runs belong to no pair).
+__global__ void routed_plan_kernel(const int* __restrict__ chosen, int pairs, int E, int BM, int pad_runs, int* __restrict__ place,
                                    int* __restrict__ sorted_pair, int* __restrict__ plan, int* __restrict__ tiles) {
     pdl_wait();
     pdl_launch_dependents();
@@ -85,7 +86,7 @@ __global__ void routed_plan_kernel(const int* __restrict__ chosen, int pairs, in
         for (int e = 0; e < E; ++e) {
             offset[e] = at;
             tile_base[e] = tiles_at;
-            at += count[e];
+            at += pad_runs ? (count[e] + BM - 1) / BM * BM : count[e];
             tiles_at += (count[e] + BM - 1) / BM;
         }
         offset[E] = at;
@@ -108,15 +109,15 @@ __global__ void routed_plan_kernel(const int* __restrict__ chosen, int pairs, in
         const int e = chosen[p];
         const int at = offset[e] + atomicAdd(&count[e], 1);
         place[p] = at;
-        sorted_pair[at] = p;
+        if (!pad_runs) sorted_pair[at] = p;
     }
 }
 
-KVB_API int kvb_routed_plan(const int* chosen, int pairs, int E, int BM, int* place, int* sorted_pair, int* plan, int* tiles,
-                            cudaStream_t stream) {
+KVB_API int kvb_routed_plan(const int* chosen, int pairs, int E, int BM, int pad_runs, int* place, int* sorted_pair, int* plan,
+                            int* tiles, cudaStream_t stream) {
     if (pairs <= 0) return KVB_OK;
     if (E < 1 || E > MOE_MAX_EXPERTS || BM < 1) return KVB_ERR_SHAPE;
-    kvb_launch(routed_plan_kernel, dim3(1), dim3(1024), 0, stream, chosen, pairs, E, BM, place, sorted_pair, plan, tiles);
+    kvb_launch(routed_plan_kernel, dim3(1), dim3(1024), 0, stream, chosen, pairs, E, BM, pad_runs, place, sorted_pair, plan, tiles);
     return kvb_launch_status();
 }
 

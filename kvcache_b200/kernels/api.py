@@ -118,9 +118,14 @@ _SIGNATURES = {
                              _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
                              _c_void_p, _c_void_p],
     },
+    "gemm_grouped": {
+        "kvb_gather_rows": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+        "kvb_grouped_gemm_tcgen05": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                     _c_int, _c_void_p, _c_void_p],
+    },
     "moe": {
         "kvb_route_top": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
-        "kvb_routed_plan": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+        "kvb_routed_plan": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
         "kvb_grouped_gemm": [_c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
                              _c_int, _c_int, _c_int, _c_void_p],
         "kvb_routed_combine": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
@@ -228,6 +233,10 @@ class CudaKernels(KernelSet):
         self._latent = _Library("latent")
         self._moe = _Library("moe")
         self._latent_flash = _Library("latent_flash")
+        self._gemm_grouped = _Library("gemm_grouped")
+        # Steps with at least this many (row, choice) pairs run the routed feed-forward's products through the tensor-memory
+        # kernel (bfloat16, widths in steps of 8): tiles of 128 rows per expert only pay when experts have that many rows.
+        self.routed_tcgen05_min_pairs: Optional[int] = 1024
         self.latent_flash = True             # bfloat16, key rows in steps of 8 numbers: the tensor-core kernel over shared key rows
         self._latent_planners: Dict[int, "LatentAttentionPlanner"] = {}
         self._sampling = _Library("sampling")
@@ -797,18 +806,41 @@ class CudaKernels(KernelSet):
         E, F, _ = w_up.shape
         top = chosen.shape[1]
         pairs = T * top
-        BM = 16 if pairs <= self.ROUTED_SMALL_PAIRS else 64
-        max_tiles = -(-pairs // BM) + E
         ws, i32 = workspace, torch.int32
+        code, stream = _dtype_code(x.dtype), self._stream()
         place = ws.buffer("moe.place", (pairs,), i32)
         order = ws.buffer("moe.order", (pairs,), i32)
         plan = ws.buffer("moe.plan", (4,), i32)
+        if (self.routed_tcgen05_min_pairs is not None and pairs >= self.routed_tcgen05_min_pairs and x.dtype == torch.bfloat16
+                and H % 8 == 0 and F % 8 == 0):
+            # Many rows: runs padded to tiles of 128 rows, the step's rows gathered into that order, both products on tcgen05.
+            BM = 128
+            max_tiles = -(-pairs // BM) + E
+            capacity = max_tiles * BM
+            tiles = ws.buffer("moe.tiles", (max_tiles * 3,), i32)
+            xs = ws.buffer("moe.xs", (capacity, H), x.dtype)
+            act = ws.buffer("moe.act", (capacity, F), x.dtype)
+            y = ws.buffer("moe.y", (capacity, H), x.dtype)
+            self._count("routed_plan")
+            _check(self._moe.kvb_routed_plan(_ptr(chosen), pairs, E, BM, 1, _ptr(place), _ptr(order), _ptr(plan), _ptr(tiles), stream),
+                   "routed_plan")
+            self._count("gather_rows")
+            _check(self._gemm_grouped.kvb_gather_rows(_ptr(x), _ptr(place), _ptr(xs), pairs, top, H, stream), "gather_rows")
+            for a, w, out_, n, k, act_code, what in ((xs, w_up, act, F, H, 1, "up"), (act, w_down, y, H, F, 0, "down")):
+                self._count("grouped_gemm_tcgen05")
+                _check(self._gemm_grouped.kvb_grouped_gemm_tcgen05(_ptr(a), _ptr(w), _ptr(out_), _ptr(plan), _ptr(tiles), max_tiles,
+                                                                   capacity, E, n, k, act_code, _ptr(self.error_word), stream),
+                       f"grouped_gemm_tcgen05 ({what})")
+            self._count("routed_combine")
+            _check(self._moe.kvb_routed_combine(code, _ptr(y), _ptr(place), _ptr(share), _ptr(out), T, top, H, stream), "routed_combine")
+            return
+        BM = 16 if pairs <= self.ROUTED_SMALL_PAIRS else 64
+        max_tiles = -(-pairs // BM) + E
         tiles = ws.buffer("moe.tiles", (max_tiles * 3,), i32)
         act = ws.buffer("moe.act", (pairs, F), x.dtype)
         y = ws.buffer("moe.y", (pairs, H), x.dtype)
-        code, stream = _dtype_code(x.dtype), self._stream()
         self._count("routed_plan")
-        _check(self._moe.kvb_routed_plan(_ptr(chosen), pairs, E, BM, _ptr(place), _ptr(order), _ptr(plan), _ptr(tiles), stream),
+        _check(self._moe.kvb_routed_plan(_ptr(chosen), pairs, E, BM, 0, _ptr(place), _ptr(order), _ptr(plan), _ptr(tiles), stream),
                "routed_plan")
         self._count("grouped_gemm")
         _check(self._moe.kvb_grouped_gemm(code, _ptr(x), _ptr(order), top, _ptr(w_up), _ptr(act), _ptr(plan), _ptr(tiles),

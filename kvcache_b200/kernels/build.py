@@ -33,6 +33,7 @@ MODULES: Dict[str, dict] = {
     "latent": {"src": "latent.cu", "deps": ["common.cuh", "mma_tile.cuh"]},
     "moe": {"src": "moe.cu", "deps": ["common.cuh", "mma_tile.cuh"]},
     "latent_flash": {"src": "latent_flash.cu", "deps": ["common.cuh"]},
+    "gemm_grouped": {"src": "gemm_grouped.cu", "deps": ["common.cuh", "tc_common.cuh"]},
     "sampling": {"src": "sampling.cu", "deps": ["common.cuh"]},
     "gemm_skinny": {"src": "gemm_skinny.cu", "deps": ["common.cuh"]},
     "gemm_tcgen05": {"src": "gemm_tcgen05.cu", "deps": ["common.cuh", "tc_common.cuh"]},

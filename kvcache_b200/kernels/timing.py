@@ -52,7 +52,7 @@ class KernelTiming:
     def __init__(self, kernels, hold_ms: float = 4.0):
         self.kernels = kernels
         self.hold_cycles = int(hold_ms * 1e-3 * getattr(torch.cuda.get_device_properties(kernels.device), "clock_rate", 1_900_000) * 1e3) if hold_ms > 0 else 0
-        self.records: List[tuple] = []      # (class, bytes, begin event, end event, launches)
+        self.records: List[tuple] = []      # (class, bytes, begin event, end event, launches, flops)
         self._saved: Dict[str, Callable] = {}
         self._depth = 0
 
@@ -107,6 +107,38 @@ class KernelTiming:
             return f"routed_experts {w_up.shape[0]}x{w_up.shape[1]}x{w_up.shape[2]}", used * per_expert + _numel_bytes(x) + _numel_bytes(out)
         return name, 0
 
+    @staticmethod
+    def _keys_seen(batch) -> int:
+        """Sum over the step's rows of the keys a row sees (its own included), without windows."""
+        host = batch.host
+        if "starts" not in host:
+            return batch.num_tokens * batch.max_kv_len
+        return int(sum(int(c) * int(s) + int(c) * (int(c) + 1) // 2 for s, c in zip(host["starts"], host["counts"])))
+
+    @classmethod
+    def _flops(cls, name: str, args, kwargs) -> int:
+        """Multiply-adds times two that the call's matrix products need (0 for classes that are only moved bytes)."""
+        if name == "linear":
+            return 2 * args[0].shape[0] * args[1].shape[0] * args[1].shape[1]
+        if name == "gate_up_act":
+            return 2 * args[0].shape[0] * args[1].shape[0] * args[1].shape[1]
+        if name == "head_linear":
+            w = args[1]
+            return 2 * args[0].shape[0] * w.shape[0] * w.shape[1] * w.shape[2]
+        if name == "latent_attention":
+            batch, kv, heads, value_dim = args[1], args[2], args[4], args[5]
+            return 2 * heads * (kv.spec.head_dim + value_dim) * cls._keys_seen(batch)
+        if name == "paged_attention":
+            batch, kv, heads = args[1], args[2], args[4]
+            return 4 * heads * kv.spec.head_dim * cls._keys_seen(batch)
+        if name == "rope_append_attention":
+            batch, kv, heads = args[4], args[5], args[7]
+            return 4 * heads * kv.spec.head_dim * cls._keys_seen(batch)
+        if name == "routed_experts":
+            x, w_up, chosen = args[0], args[1], args[3]
+            return 2 * chosen.numel() * 2 * w_up.shape[1] * w_up.shape[2]
+        return 0
+
     # ---- switching on and off -------------------------------------------------------------------------
     def start(self) -> None:
         for name in self.OPERATORS:
@@ -121,6 +153,7 @@ class KernelTiming:
             if self._depth:                              # called by an operator that is being timed: part of its class
                 return original(*args, **kwargs)
             label, nbytes = self._describe(name, args, kwargs)
+            flops = self._flops(name, args, kwargs)
             if name == "embed" and self.hold_cycles:
                 torch.cuda._sleep(self.hold_cycles)      # keeps the GPU busy while the host queues this step
             begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -134,12 +167,12 @@ class KernelTiming:
             end.record()
             if name == "rope_append_attention" and result is False:
                 return result                            # nothing ran: the caller makes the two calls
-            self.records.append((label, nbytes, begin, end, self.kernels.launches - launches))
+            self.records.append((label, nbytes, begin, end, self.kernels.launches - launches, flops))
             return result
         return timed
 
     def stop(self) -> Dict[str, dict]:
-        """Restores the operators; returns {class: {"us", "bytes", "calls", "launches"}} summed over all calls."""
+        """Restores the operators; returns {class: {"us", "bytes", "calls", "launches", "flops"}} summed over all calls."""
         for name in self._saved:
             try:
                 delattr(self.kernels, name)              # the wrapper lives on the instance; the class method is back
@@ -148,8 +181,9 @@ class KernelTiming:
         self._saved.clear()
         torch.cuda.synchronize(self.kernels.device)
         report: Dict[str, dict] = {}
-        for label, nbytes, begin, end, launches in self.records:
-            entry = report.setdefault(label, {"us": 0.0, "bytes": 0, "calls": 0, "launches": 0})
+        for label, nbytes, begin, end, launches, flops in self.records:
+            entry = report.setdefault(label, {"us": 0.0, "bytes": 0, "calls": 0, "launches": 0, "flops": 0})
+            entry["flops"] += flops
             entry["us"] += begin.elapsed_time(end) * 1e3
             entry["bytes"] += nbytes
             entry["calls"] += 1

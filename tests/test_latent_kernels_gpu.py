@@ -209,9 +209,10 @@ def test_route_top(kernels, E, top):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T", [1, 5, 200])
-@pytest.mark.parametrize("shape", [(16, 2, 64, 192), (5, 1, 40, 72), (6, 6, 24, 100)])      # experts, top, ff, width
+@pytest.mark.parametrize("T", [1, 5, 200, 700])
+@pytest.mark.parametrize("shape", [(16, 2, 64, 192), (5, 1, 40, 72), (6, 6, 24, 100), (7, 3, 328, 136)])      # experts, top, ff, width
 def test_routed_experts(kernels, dtype, T, shape):
+    """700 rows with two or more choices each reach the tensor-memory products (bfloat16, widths in steps of 8)."""
     E, top, F, H = shape
     x = _rand(T, H, dtype=dtype, seed=1)
     w_up, w_down = _rand(E, F, H, dtype=dtype, seed=2, scale=H ** -0.5), _rand(E, H, F, dtype=dtype, seed=3, scale=F ** -0.5)
