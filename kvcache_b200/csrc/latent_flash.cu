@@ -159,6 +159,7 @@ __global__ void __launch_bounds__(THREADS) latent_flash_kernel(
         float s[MT][4];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) s[mt][0] = s[mt][1] = s[mt][2] = s[mt][3] = 0.f;
+#pragma unroll 3
         for (int k2 = 0; k2 < KS2; ++k2) {
             uint32_t b[4];
             ldmatrix_x4(b[0], b[1], b[2], b[3], Kt + (size_t)(8 * warp + (lane & 7)) * L.rs + k2 * 32 + (lane >> 3) * 8);
@@ -290,31 +291,64 @@ __global__ void __launch_bounds__(THREADS) latent_flash_kernel(
         }
 }
 
-// out[row] = sum_s 2^(m_s - M) O_s[row] / sum_s 2^(m_s - M) l_s over the `nsplit` items of the row's tile, in the
-// order of the splits.  Grid (tiles, BM); the items of tile i are i * nsplit .. (i + 1) * nsplit - 1.
+// out[row] = sum_s 2^(m_s - M) O_s[row] / sum_s 2^(m_s - M) l_s over the `nsplit` items of the row's tile.
+// Grid (tiles, BM); the items of tile i are i * nsplit .. (i + 1) * nsplit - 1.  A block is MERGE_GROUPS x Dv / 4 threads:
+// thread (g, c) adds four columns of the splits g, g + MERGE_GROUPS, ... (independent loads, all in flight at once), and the
+// groups' sums are added in the order of the groups - a fixed order, whichever block runs first.
+constexpr int MAX_SPLITS = 32, MERGE_GROUPS = 8;
 __global__ void latent_flash_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                           const int* __restrict__ items, const int* __restrict__ seg_q_start,
                                           const int* __restrict__ seg_q_len, bf16* __restrict__ out, int H, int Dv, int BM,
                                           int nsplit) {
-    pdl_wait();
-    pdl_launch_dependents();
+    __shared__ float weight[MAX_SPLITS];
+    __shared__ float inv_s;
+    extern __shared__ float4 sums[];                     // [MERGE_GROUPS][Dv / 4]
     const int first = blockIdx.x * nsplit, r = blockIdx.y;
     const int seg = items[4 * first], m0 = items[4 * first + 1];
+    const int cols = Dv >> 2;
+    const int g = threadIdx.x / cols, c = threadIdx.x - g * cols;
+    pdl_wait();
+    pdl_launch_dependents();
     if (m0 + r >= seg_q_len[seg] * H) return;
-    float M = MASKED;
-    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_ml[((size_t)(first + s) * BM + r) * 2]);
-    float l = 0.f;
-    for (int s = 0; s < nsplit; ++s) {
-        const float* ml = part_ml + ((size_t)(first + s) * BM + r) * 2;
-        l += exp2f(ml[0] - M) * ml[1];
+    const float4* base = reinterpret_cast<const float4*>(part_o + ((size_t)first * BM + r) * Dv) + c;
+    const size_t step = (size_t)BM * cols;
+    float4 v[MAX_SPLITS / MERGE_GROUPS];
+#pragma unroll
+    for (int i = 0; i < MAX_SPLITS / MERGE_GROUPS; ++i) {
+        const int s = g + i * MERGE_GROUPS;
+        v[i] = s < nsplit ? base[(size_t)s * step] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    const float inv = l > 0.f ? 1.f / l : 0.f;
-    bf16* orow = out + ((size_t)seg_q_start[seg] * H + m0 + r) * Dv;
-    for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
-        float acc = 0.f;
-        for (int s = 0; s < nsplit; ++s)
-            acc += exp2f(part_ml[((size_t)(first + s) * BM + r) * 2] - M) * part_o[((size_t)(first + s) * BM + r) * Dv + d];
-        orow[d] = __float2bfloat16_rn(acc * inv);
+    if (threadIdx.x < 32) {
+        const int s = threadIdx.x;
+        const float* ml = part_ml + ((size_t)(first + (s < nsplit ? s : 0)) * BM + r) * 2;
+        const float m = s < nsplit ? ml[0] : MASKED, l = s < nsplit ? ml[1] : 0.f;
+        const float M = warp_max(m);
+        const float w = exp2f(m - M);
+        weight[s] = w;
+        float total = 0.f;                               // summed in the order of the splits
+        for (int i = 0; i < nsplit; ++i) total += __shfl_sync(0xffffffffu, w * l, i);
+        if (s == 0) inv_s = total > 0.f ? 1.f / total : 0.f;
+    }
+    __syncthreads();
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < MAX_SPLITS / MERGE_GROUPS; ++i) {
+        const int s = g + i * MERGE_GROUPS;
+        const float w = s < nsplit ? weight[s] : 0.f;
+        acc.x += w * v[i].x; acc.y += w * v[i].y; acc.z += w * v[i].z; acc.w += w * v[i].w;
+    }
+    sums[g * cols + c] = acc;
+    __syncthreads();
+    if (g == 0) {
+        float4 t = sums[c];
+        for (int k = 1; k < MERGE_GROUPS; ++k) {
+            const float4 u = sums[k * cols + c];
+            t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+        }
+        const float inv = inv_s;
+        bf16* orow = out + ((size_t)seg_q_start[seg] * H + m0 + r) * Dv + 4 * c;
+        *reinterpret_cast<__nv_bfloat162*>(orow) = __floats2bfloat162_rn(t.x * inv, t.y * inv);
+        *reinterpret_cast<__nv_bfloat162*>(orow + 2) = __floats2bfloat162_rn(t.z * inv, t.w * inv);
     }
 }
 
@@ -345,7 +379,7 @@ static int launch(const bf16* q, bf16* out, const bf16* k_pages, const int* bloc
 
 // Whether the kernel takes these sizes (else the caller uses the generic kernel): 0 yes, negative no.
 KVB_API int kvb_latent_flash_supports(int Dk, int Dv, int BM) {
-    if (Dk % 8 != 0 || Dk < 8 || Dv < 2 || Dv % 2 != 0 || Dv > Dk || Dv > 512 || (BM != 16 && BM != 64)) return KVB_ERR_SHAPE;
+    if (Dk % 8 != 0 || Dk < 8 || Dv < 4 || Dv % 4 != 0 || Dv > Dk || Dv > 512 || (BM != 16 && BM != 64)) return KVB_ERR_SHAPE;
     const int NV = Dv <= 64 ? 1 : (Dv <= 128 ? 2 : (Dv <= 256 ? 4 : 8));
     return lf::make_layout(BM / 16, NV, Dk, 1).total <= 220 * 1024 ? KVB_OK : KVB_ERR_LIMIT;
 }
@@ -359,7 +393,7 @@ KVB_API int kvb_latent_flash(const void* q, void* out, const void* k_pages, cons
     if (n_items <= 0) return KVB_OK;
     const int ok = kvb_latent_flash_supports(Dk, Dv, BM);
     if (ok != KVB_OK) return ok;
-    if (nsplit < 1 || n_tiles * nsplit != n_items || (nsplit > 1 && (!part_o || !part_ml))) return KVB_ERR_SHAPE;
+    if (nsplit < 1 || nsplit > lf::MAX_SPLITS || n_tiles * nsplit != n_items || (nsplit > 1 && (!part_o || !part_ml))) return KVB_ERR_SHAPE;
     const int NV = Dv <= 64 ? 1 : (Dv <= 128 ? 2 : (Dv <= 256 ? 4 : 8));
     int code = KVB_ERR_SHAPE;
 #define KVB_LF(MT, NV_)                                                                                                      \
@@ -373,7 +407,7 @@ KVB_API int kvb_latent_flash(const void* q, void* out, const void* k_pages, cons
     }
 #undef KVB_LF
     if (code != KVB_OK || nsplit == 1) return code;
-    kvb_launch(lf::latent_flash_merge_kernel, dim3(n_tiles, BM), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml,
+    kvb_launch(lf::latent_flash_merge_kernel, dim3(n_tiles, BM), dim3(lf::MERGE_GROUPS * (Dv / 4)), (size_t)lf::MERGE_GROUPS * Dv * 4, stream, (const float*)part_o, (const float*)part_ml,
                items, seg_q_start, seg_q_len, (bf16*)out, H, Dv, BM, nsplit);
     return kvb_launch_status();
 }

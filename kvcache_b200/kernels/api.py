@@ -238,7 +238,7 @@ class CudaKernels(KernelSet):
         # kernel (bfloat16, widths in steps of 8): tiles of 128 rows per expert only pay when experts have that many rows.
         self.routed_tcgen05_min_pairs: Optional[int] = 1024
         self.latent_flash = True             # bfloat16, key rows in steps of 8 numbers: the tensor-core kernel over shared key rows
-        self._latent_planners: Dict[int, "LatentAttentionPlanner"] = {}
+        self._latent_planners: Dict[tuple, "LatentAttentionPlanner"] = {}
         self._sampling = _Library("sampling")
         self._gemm_skinny = _Library("gemm_skinny")
         self._gemm_tc = _Library("gemm_tcgen05")
@@ -361,11 +361,21 @@ class CudaKernels(KernelSet):
             self._attention_planner = PagedAttentionPlanner()
         return self._attention_planner
 
-    def latent_attention_planner(self, heads: int) -> LatentAttentionPlanner:
-        """The work list `latent_attention` reads from `StepBatch.plans` for mixers of `heads` heads (one planner for all of them)."""
-        found = self._latent_planners.get(heads)
+    def _latent_blocks_wanted(self, key_dim: int, value_dim: int) -> int:
+        """As many blocks as the GPU holds at once of the kernel's form for decoded tokens (tiles of 16 rows, two key stages):
+        two an SM while their shared memory allows (csrc/latent_flash.cu, make_layout), else one - a second wave of blocks
+        costs more than longer runs of keys per block (8 requests of 4,096 tokens, rows of 576: 20.0 us with 144 blocks, 22.9 with 256)."""
+        dk_pad = -(-key_dim // 32) * 32
+        row = max(dk_pad, 64 * (1 if value_dim <= 64 else 2 if value_dim <= 128 else 4 if value_dim <= 256 else 8)) + 8
+        smem = 16 * (dk_pad + 8) * 2 + 2 * 64 * row * 2 + 16 * 68 * 4 + 16 * 72 * 2 + 256
+        return (2 if 2 * smem <= 220 * 1024 else 1) * self.sm_count
+
+    def latent_attention_planner(self, heads: int, key_dim: int, value_dim: int) -> LatentAttentionPlanner:
+        """The work list `latent_attention` reads from `StepBatch.plans` for mixers of these sizes (one planner for all of them)."""
+        key = (heads, self._latent_blocks_wanted(key_dim, value_dim))
+        found = self._latent_planners.get(key)
         if found is None:
-            found = self._latent_planners[heads] = LatentAttentionPlanner(heads, 2 * self.sm_count)
+            found = self._latent_planners[key] = LatentAttentionPlanner(*key)
         return found
 
     # ---- operators ---------------------------------------------------------
@@ -768,7 +778,7 @@ class CudaKernels(KernelSet):
         share; a row's value is the first `value_dim` numbers of its key.  q [T, H * key_dim], out [T, H * value_dim]."""
         T = q.shape[0]
         spec = kv.spec
-        plan = batch.plans.get(f"latent_attention.h{num_heads}")
+        plan = batch.plans.get(LatentAttentionPlanner.plan_name(num_heads, self._latent_blocks_wanted(spec.head_dim, value_dim)))
         if (self.latent_flash and q.dtype == torch.bfloat16 and plan is not None and workspace is not None and spec.num_kv_heads == 1
                 and self._latent_flash.kvb_latent_flash_supports(spec.head_dim, value_dim, plan.counts["bm"]) == 0):
             n, tiles, nsplit, bm = (plan.counts[k] for k in ("items", "tiles", "nsplit", "bm"))

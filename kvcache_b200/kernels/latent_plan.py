@@ -47,7 +47,11 @@ def _plan(segments: tuple, heads: int, blocks_wanted: int):
 class LatentAttentionPlanner(StepPlanner):
     def __init__(self, heads: int, blocks_wanted: int):
         self.heads, self.blocks_wanted = heads, blocks_wanted
-        self.name = f"latent_attention.h{heads}"
+        self.name = self.plan_name(heads, blocks_wanted)
+
+    @staticmethod
+    def plan_name(heads: int, blocks_wanted: int) -> str:
+        return f"latent_attention.h{heads}.b{blocks_wanted}"
 
     def sections(self, num_tokens: int, num_segments: int) -> Dict[str, int]:
         tiles = num_tokens * self.heads // LARGE_TILE + 2 * num_segments

@@ -82,7 +82,7 @@ class LatentAttention(Mixer):
 
     def step_planners(self, kernels):
         planner = getattr(kernels, "latent_attention_planner", None)
-        return () if planner is None else (planner(self.num_heads),)
+        return () if planner is None else (planner(self.num_heads, self.key_dim, self.kv_rank),)
 
     def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
         T, H = x.shape[0], self.num_heads

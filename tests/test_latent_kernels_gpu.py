@@ -100,12 +100,15 @@ def test_head_linear(kernels, dtype, T, shape):
         assert_close(got, ref, TOL[dtype], form)
 
 
-def _with_latent_plan(batch, segments, heads, blocks_wanted=296):
-    """Adds the work list of the tensor-core kernel over shared key rows to a hand-made batch."""
+def _with_latent_plan(batch, segments, heads, blocks_wanted=None, kernels=None, dims=None):
+    """Adds the work list of the tensor-core kernel over shared key rows to a hand-made batch: made for `blocks_wanted`
+    blocks, under the name the kernel set looks it up by."""
     import dataclasses
     from kvcache_b200.kernels.latent_plan import LatentAttentionPlanner
     from kvcache_b200.parts.base import StepPlan
-    planner = LatentAttentionPlanner(heads, blocks_wanted)
+    name = LatentAttentionPlanner.plan_name(heads, kernels._latent_blocks_wanted(*dims))
+    planner = LatentAttentionPlanner(heads, blocks_wanted or kernels._latent_blocks_wanted(*dims))
+    planner.name = name
     arrays, counts = planner.plan(np.asarray([s for s, _ in segments]), np.asarray([n for _, n in segments]))
     plans = dict(batch.plans)
     plans[planner.name] = StepPlan({k: torch.tensor(np.array(v), dtype=torch.int32) for k, v in arrays.items()}, counts)
@@ -119,7 +122,7 @@ FLASH_SEGMENTS = {"decode": [(70, 1), (129, 1), (0, 1), (1000, 1)], "prompt": [(
                   "mixed": [(0, 33), (70, 1), (15, 2), (129, 1), (300, 130)]}
 
 
-@pytest.mark.parametrize("wanted", [296, 4])
+@pytest.mark.parametrize("wanted", [None, 4])
 @pytest.mark.parametrize("kind", list(FLASH_SEGMENTS))
 @pytest.mark.parametrize("case", FLASH_CASES)
 def test_latent_attention_tensor_cores(kernels, case, kind, wanted):
@@ -129,7 +132,7 @@ def test_latent_attention_tensor_cores(kernels, case, kind, wanted):
     segments = FLASH_SEGMENTS[kind]
     dtype = torch.bfloat16
     batch, kv = paged_scenario(segments, num_kv_heads=1, head_dim=D, page_size=page, dtype=dtype, device="cpu", seed=5)
-    batch = _with_latent_plan(batch, segments, H, wanted)
+    batch = _with_latent_plan(batch, segments, H, wanted, kernels, (D, Dv))
     T = batch.num_tokens
     q = _rand(T, H * D, dtype=dtype, seed=6)
     ref, got = torch.zeros(T, H * Dv, dtype=dtype), torch.full((T, H * Dv), 7.0, dtype=dtype, device=DEV)
@@ -148,7 +151,7 @@ def test_latent_attention_tensor_cores_one_far_key(kernels):
     segments = [(900, 1), (0, 200)]
     dtype = torch.bfloat16
     batch, kv = paged_scenario(segments, num_kv_heads=1, head_dim=D, page_size=page, dtype=dtype, device="cpu", seed=9)
-    batch = _with_latent_plan(batch, segments, H)
+    batch = _with_latent_plan(batch, segments, H, None, kernels, (D, Dv))
     q = _rand(batch.num_tokens, H * D, dtype=dtype, seed=10, scale=0.02)
     probes = [(0, 0, 2, 15), (0, 0, 3, 16), (0, 0, 5, 640), (1, 150, 1, 63), (1, 199, 4, 64), (1, 77, 0, 77)]   # segment, token, head, key
     for seg, tok, head, key in probes:
