@@ -14,7 +14,7 @@
 #include "common.cuh"
 
 #define ATTN_THREADS 128
-#define ATTN_MAX_D 1024
+#define ATTN_MAX_D 2048
 
 template <typename T>
 __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,

@@ -49,9 +49,9 @@ KAKI_Q = {
 KAKI_R = {
     "architecture": "Kakipel", "vocab": 500, "width": 120, "norm": {"eps": 1e-5},
     "layers": [
-        _layer(_mixer(5, 48, 16, 32, 72, 56, 0.125, 250000.0, (2.0, 128, 32.0, 1.0)), MOE(9, 3, 40)),
-        _layer(_mixer(5, 48, 16, 32, 72, 56, 0.125, 250000.0, (2.0, 128, 32.0, 1.0)), DENSE(136)),
-        _layer(_mixer(5, 48, 16, 32, 72, 56, 0.125, 250000.0, (2.0, 128, 32.0, 1.0)), MOE(9, 3, 40)),
+        _layer(_mixer(5, 48, 16, 32, 72, 56, 0.125, 300000.0, (2.5, 128, 24.0, 1.5)), MOE(9, 3, 40)),
+        _layer(_mixer(5, 48, 16, 32, 72, 56, 0.125, 300000.0, (2.5, 128, 24.0, 1.5)), DENSE(136)),
+        _layer(_mixer(5, 48, 16, 32, 72, 56, 0.125, 300000.0, (2.5, 128, 24.0, 1.5)), MOE(9, 3, 40)),
     ],
     "loop": {"start": 1, "stop": 2, "times": 3},
 }

@@ -30,7 +30,7 @@ def test_config_round_trip_and_layer_runs():
         assert [(i, t, o) for i, t, o in c.layer_runs()] == plain.layer_runs(config_dict(name))
     c = config_from_dict(config_dict("R"))
     assert [i for i, _, _ in c.layer_runs()] == [0, 1, 1, 1, 2] and [t for _, t, _ in c.layer_runs()] == [None, 0, 1, 2, None]
-    assert c.layers[0].mlp.experts == 9 and c.layers[1].mlp.kind == "dense" and c.layers[0].mixer.rot.scaling.factor == 2.0
+    assert c.layers[0].mlp.experts == 9 and c.layers[1].mlp.kind == "dense" and c.layers[0].mixer.rot.scaling.factor == 2.5
 
 
 def test_config_faults_are_all_reported():
@@ -71,7 +71,7 @@ def test_cache_holds_one_row_per_token_and_no_values(tmp_path):
 
 
 # ---- mechanisms alone ---------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("rot", [{"base": 250000.0, "dims": 32, "scaling": {"factor": 2.0, "original": 128, "fast": 32.0, "slow": 1.0}},
+@pytest.mark.parametrize("rot", [{"base": 300000.0, "dims": 28, "scaling": {"factor": 2.5, "original": 128, "fast": 24.0, "slow": 1.5}},
                                  {"base": 100.0, "dims": 6}, {"base": 3000.0, "dims": 12, "scaling": {"factor": 3.0, "original": 48, "fast": 4.0, "slow": 0.5}},
                                  {"base": 10000.0, "dims": 64, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}])
 def test_rotation_tables(rot):
