@@ -61,7 +61,7 @@ __host__ __device__ inline Layout make_layout(int MT, int NV, int Dk, int nstage
     const int dv_pad = 64 * NV;
     L.qs = L.dk_pad + 8;
     L.rs = (L.dk_pad > dv_pad ? L.dk_pad : dv_pad) + 8;
-    L.ss = BN + 4;
+    L.ss = BN + 8;
     L.ps = BN + 8;
     size_t at = 0;
     L.q_off = at;  at += (size_t)BM * L.qs * 2;
@@ -73,8 +73,10 @@ __host__ __device__ inline Layout make_layout(int MT, int NV, int Dk, int nstage
     return L;
 }
 
+// Tiles of 64 rows with values of up to 256 numbers are held to 128 registers, so that two blocks share an SM and one's copies
+// and softmax overlap the other's products.
 template <int MT, int NV>
-__global__ void __launch_bounds__(THREADS) latent_flash_kernel(
+__global__ void __launch_bounds__(THREADS, (MT == 4 && NV <= 4) ? 2 : 1) latent_flash_kernel(
     const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ k_pages, const int* __restrict__ block_table,
     int table_stride, const int* __restrict__ items, const int* __restrict__ seg_q_start, const int* __restrict__ seg_q_len,
     const int* __restrict__ seg_kv_len, float* __restrict__ part_o, float* __restrict__ part_ml, int H, int Dk, int Dv,
@@ -176,12 +178,22 @@ __global__ void __launch_bounds__(THREADS) latent_flash_kernel(
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int r = mt * 16 + g + (i >> 1) * 8;
-                const int c = 8 * warp + 2 * t4 + (i & 1);
-                const int j = key0 + c, pos = rowpos[r];
-                const bool seen = j < ke && j <= pos && (window <= 0 || j > pos - window);
-                Ss[r * L.ss + c] = seen ? s[mt][i] * scale_log2 : MASKED;
+            for (int hi = 0; hi < 2; ++hi) {             // rows g and g + 8: two columns each, stored as one 8-byte word
+                const int r = mt * 16 + g + hi * 8;
+                const int c = 8 * warp + 2 * t4;
+                const int pos = rowpos[r];
+                float2 v;
+                {
+                    const int j = key0 + c;
+                    const bool seen = j < ke && j <= pos && (window <= 0 || j > pos - window);
+                    v.x = seen ? s[mt][2 * hi] * scale_log2 : MASKED;
+                }
+                {
+                    const int j = key0 + c + 1;
+                    const bool seen = j < ke && j <= pos && (window <= 0 || j > pos - window);
+                    v.y = seen ? s[mt][2 * hi + 1] * scale_log2 : MASKED;
+                }
+                *reinterpret_cast<float2*>(Ss + r * L.ss + c) = v;
             }
         }
         __syncthreads();
@@ -193,20 +205,33 @@ __global__ void __launch_bounds__(THREADS) latent_flash_kernel(
             float v[CPT];
             float mx = MASKED;
 #pragma unroll
-            for (int i = 0; i < CPT; ++i) {
-                v[i] = Ss[r * L.ss + c0 + i];
-                mx = fmaxf(mx, v[i]);
+            for (int i = 0; i < CPT; i += 4) {
+                const float4 f = *reinterpret_cast<const float4*>(Ss + r * L.ss + c0 + i);
+                v[i] = f.x; v[i + 1] = f.y; v[i + 2] = f.z; v[i + 3] = f.w;
             }
+#pragma unroll
+            for (int i = 0; i < CPT; ++i) mx = fmaxf(mx, v[i]);
 #pragma unroll
             for (int d = TPR / 2; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
             const float m_old = m_run[r];
             const float m_new = fmaxf(m_old, mx);
             float sum = 0.f;
+            uint32_t packed[CPT / 2];
 #pragma unroll
-            for (int i = 0; i < CPT; ++i) {
-                const float p = v[i] > 0.5f * MASKED ? exp2f(v[i] - m_new) : 0.f;
-                sum += p;
-                Ps[r * L.ps + c0 + i] = __float2bfloat16_rn(p);
+            for (int i = 0; i < CPT; i += 2) {
+                const float p0 = v[i] > 0.5f * MASKED ? exp2f(v[i] - m_new) : 0.f;
+                const float p1 = v[i + 1] > 0.5f * MASKED ? exp2f(v[i + 1] - m_new) : 0.f;
+                sum += p0;
+                sum += p1;
+                __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
+                packed[i / 2] = *reinterpret_cast<uint32_t*>(&pp);
+            }
+            if constexpr (CPT == 4) {
+                *reinterpret_cast<uint2*>(Ps + r * L.ps + c0) = make_uint2(packed[0], packed[1]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < CPT / 8; ++i)
+                    *reinterpret_cast<uint4*>(Ps + r * L.ps + c0 + 8 * i) = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
             }
 #pragma unroll
             for (int d = TPR / 2; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
@@ -358,9 +383,12 @@ static int launch(const bf16* q, bf16* out, const bf16* k_pages, const int* bloc
                   int H, int Dk, int Dv, int page_size, int window, float scale, int nsplit, int* err, cudaStream_t stream) {
     int nstage = 2;
     Layout L = make_layout(MT, NV, Dk, nstage);
-    if (L.total > 220 * 1024) {
+    // One stage where two stages would keep a second block off the SM (two blocks hide more than a second stage), or do not fit.
+    const Layout one = make_layout(MT, NV, Dk, 1);
+    const bool two_blocks = MT == 4 && NV <= 4;
+    if (L.total > 220 * 1024 || (two_blocks && 2 * L.total > 220 * 1024 && 2 * one.total <= 220 * 1024)) {
         nstage = 1;
-        L = make_layout(MT, NV, Dk, nstage);
+        L = one;
         if (L.total > 220 * 1024) return KVB_ERR_LIMIT;
     }
     static size_t configured = 0;                       // per instantiation
@@ -379,7 +407,7 @@ static int launch(const bf16* q, bf16* out, const bf16* k_pages, const int* bloc
 
 // Whether the kernel takes these sizes (else the caller uses the generic kernel): 0 yes, negative no.
 KVB_API int kvb_latent_flash_supports(int Dk, int Dv, int BM) {
-    if (Dk % 8 != 0 || Dk < 8 || Dv < 4 || Dv % 4 != 0 || Dv > Dk || Dv > 512 || (BM != 16 && BM != 64)) return KVB_ERR_SHAPE;
+    if (Dk % 8 != 0 || Dk < 8 || Dv < 4 || Dv % 4 != 0 || Dv > Dk || Dv > 512 || (BM != 16 && BM != 32 && BM != 64)) return KVB_ERR_SHAPE;
     const int NV = Dv <= 64 ? 1 : (Dv <= 128 ? 2 : (Dv <= 256 ? 4 : 8));
     return lf::make_layout(BM / 16, NV, Dk, 1).total <= 220 * 1024 ? KVB_OK : KVB_ERR_LIMIT;
 }
@@ -402,6 +430,8 @@ KVB_API int kvb_latent_flash(const void* q, void* out, const void* k_pages, cons
                                nsplit, err, stream)
     if (BM == 16) {
         if (NV == 1) KVB_LF(1, 1); else if (NV == 2) KVB_LF(1, 2); else if (NV == 4) KVB_LF(1, 4); else KVB_LF(1, 8);
+    } else if (BM == 32) {
+        if (NV == 1) KVB_LF(2, 1); else if (NV == 2) KVB_LF(2, 2); else if (NV == 4) KVB_LF(2, 4); else KVB_LF(2, 8);
     } else {
         if (NV == 1) KVB_LF(4, 1); else if (NV == 2) KVB_LF(4, 2); else if (NV == 4) KVB_LF(4, 4); else KVB_LF(4, 8);
     }

@@ -361,6 +361,18 @@ class CudaKernels(KernelSet):
             self._attention_planner = PagedAttentionPlanner()
         return self._attention_planner
 
+    # Tiles of 32 rows where 64 rows leave room for one key stage only: measured slower (a prompt of 2,048 tokens, 16 heads, rows
+    # of 576: 537 us with two stages beside 32 rows, 448 us with one stage beside 64 - a key tile then serves half the rows).
+    latent_small_large_tile = False
+
+    def _latent_plan_shape(self, key_dim: int, value_dim: int) -> tuple:
+        """(blocks wanted, rows of a large tile) of the attention over shared key rows at these sizes."""
+        dk_pad = -(-key_dim // 32) * 32
+        row = max(dk_pad, 64 * (1 if value_dim <= 64 else 2 if value_dim <= 128 else 4 if value_dim <= 256 else 8)) + 8
+        fits = lambda bm, stages: bm * (dk_pad + 8) * 2 + stages * 64 * row * 2 + bm * 72 * 4 + bm * 72 * 2 + bm * 16 <= 220 * 1024
+        tile = 32 if self.latent_small_large_tile and not fits(64, 2) and fits(32, 2) else 64
+        return self._latent_blocks_wanted(key_dim, value_dim), tile
+
     def _latent_blocks_wanted(self, key_dim: int, value_dim: int) -> int:
         """As many blocks as the GPU holds at once of the kernel's form for decoded tokens (tiles of 16 rows, two key stages):
         two an SM while their shared memory allows (csrc/latent_flash.cu, make_layout), else one - a second wave of blocks
@@ -372,7 +384,7 @@ class CudaKernels(KernelSet):
 
     def latent_attention_planner(self, heads: int, key_dim: int, value_dim: int) -> LatentAttentionPlanner:
         """The work list `latent_attention` reads from `StepBatch.plans` for mixers of these sizes (one planner for all of them)."""
-        key = (heads, self._latent_blocks_wanted(key_dim, value_dim))
+        key = (heads, *self._latent_plan_shape(key_dim, value_dim))
         found = self._latent_planners.get(key)
         if found is None:
             found = self._latent_planners[key] = LatentAttentionPlanner(*key)
@@ -778,7 +790,7 @@ class CudaKernels(KernelSet):
         share; a row's value is the first `value_dim` numbers of its key.  q [T, H * key_dim], out [T, H * value_dim]."""
         T = q.shape[0]
         spec = kv.spec
-        plan = batch.plans.get(LatentAttentionPlanner.plan_name(num_heads, self._latent_blocks_wanted(spec.head_dim, value_dim)))
+        plan = batch.plans.get(LatentAttentionPlanner.plan_name(num_heads, *self._latent_plan_shape(spec.head_dim, value_dim)))
         if (self.latent_flash and q.dtype == torch.bfloat16 and plan is not None and workspace is not None and spec.num_kv_heads == 1
                 and self._latent_flash.kvb_latent_flash_supports(spec.head_dim, value_dim, plan.counts["bm"]) == 0):
             n, tiles, nsplit, bm = (plan.counts[k] for k in ("items", "tiles", "nsplit", "bm"))

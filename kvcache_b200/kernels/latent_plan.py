@@ -22,10 +22,10 @@ MAX_SPLITS = 32
 
 
 @functools.lru_cache(maxsize=1024)
-def _plan(segments: tuple, heads: int, blocks_wanted: int):
+def _plan(segments: tuple, heads: int, blocks_wanted: int, large_tile: int = LARGE_TILE):
     """segments: (segment index, tokens cached, tokens brought).  Returns (int32 [items, 4]: segment, first row, first
     key, end of keys; tiles; splits per tile; rows of a tile)."""
-    bm = SMALL_TILE if all(count * heads <= SMALL_TILE for _, _, count in segments) else LARGE_TILE
+    bm = SMALL_TILE if all(count * heads <= SMALL_TILE for _, _, count in segments) else large_tile
     tiles = []
     for seg, start, count in segments:
         for m0 in range(0, count * heads, bm):
@@ -45,19 +45,21 @@ def _plan(segments: tuple, heads: int, blocks_wanted: int):
 
 
 class LatentAttentionPlanner(StepPlanner):
-    def __init__(self, heads: int, blocks_wanted: int):
-        self.heads, self.blocks_wanted = heads, blocks_wanted
-        self.name = self.plan_name(heads, blocks_wanted)
+    def __init__(self, heads: int, blocks_wanted: int, large_tile: int = LARGE_TILE):
+        """`large_tile`: rows of a tile in steps that bring more than `SMALL_TILE` rows of a request (64, or 32 where the
+        kernel's shared memory holds two key stages only beside the smaller tile)."""
+        self.heads, self.blocks_wanted, self.large_tile = heads, blocks_wanted, large_tile
+        self.name = self.plan_name(heads, blocks_wanted, large_tile)
 
     @staticmethod
-    def plan_name(heads: int, blocks_wanted: int) -> str:
-        return f"latent_attention.h{heads}.b{blocks_wanted}"
+    def plan_name(heads: int, blocks_wanted: int, large_tile: int = LARGE_TILE) -> str:
+        return f"latent_attention.h{heads}.b{blocks_wanted}.t{large_tile}"
 
     def sections(self, num_tokens: int, num_segments: int) -> Dict[str, int]:
-        tiles = num_tokens * self.heads // LARGE_TILE + 2 * num_segments
+        tiles = num_tokens * self.heads // self.large_tile + 2 * num_segments
         return {"items": 4 * max(tiles, self.blocks_wanted + num_segments)}
 
     def plan(self, starts, counts) -> Tuple[Dict[str, np.ndarray], Dict[str, int]]:
         segments = tuple((i, int(s), int(c)) for i, (s, c) in enumerate(zip(starts, counts)))
-        items, tiles, nsplit, bm = _plan(segments, self.heads, self.blocks_wanted)
+        items, tiles, nsplit, bm = _plan(segments, self.heads, self.blocks_wanted, self.large_tile)
         return {"items": items.reshape(-1)}, {"items": len(items), "tiles": tiles, "nsplit": nsplit, "bm": bm}

@@ -106,8 +106,9 @@ def _with_latent_plan(batch, segments, heads, blocks_wanted=None, kernels=None, 
     import dataclasses
     from kvcache_b200.kernels.latent_plan import LatentAttentionPlanner
     from kvcache_b200.parts.base import StepPlan
-    name = LatentAttentionPlanner.plan_name(heads, kernels._latent_blocks_wanted(*dims))
-    planner = LatentAttentionPlanner(heads, blocks_wanted or kernels._latent_blocks_wanted(*dims))
+    wanted, tile = kernels._latent_plan_shape(*dims)
+    name = LatentAttentionPlanner.plan_name(heads, wanted, tile)
+    planner = LatentAttentionPlanner(heads, blocks_wanted or wanted, tile)
     planner.name = name
     arrays, counts = planner.plan(np.asarray([s for s, _ in segments]), np.asarray([n for _, n in segments]))
     plans = dict(batch.plans)
