@@ -53,12 +53,17 @@ def build_kakipel(config: KakipelConfig, dtype: str = "bfloat16", device: str = 
                                 dtype=dtype)
         blocks.append(SandwichBlock(c.width, RMSNorm(c.width, c.norm_eps, p + "norm1"), mixer,
                                     RMSNorm(c.width, c.norm_eps, p + "norm1b"), pre2, ffn, post2, dtype))
+    # A checkpoint may carry the norms of a feed-forward that a layer does not have, or the loop's tensors without a loop:
+    # they are left alone (with a line on standard error), not an error.
+    unused = [f"l{i}.{name}" for i, layer in enumerate(c.layers) if layer.mlp is None for name in ("norm2", "norm2b")]
+    if c.loop is None:
+        unused += ["loop.in", "loop.step"]
     stream_parts = [LoopEntry(c.width, c.loop.times, "loop.in", "loop.step", dtype)] if c.loop is not None else []
     # Every layer run has a cache entry of its own: a looped layer's passes see different keys.
     schedule = [LayerCall(layer, run, True, (0, t) if opens else None) for run, (layer, t, opens) in enumerate(c.layer_runs())]
     return DecoderModel(config=c, dtype=dtype, vocab_size=c.vocab_size, width=c.width, embed_name="embed", head_name="head",
                         blocks=blocks, schedule=schedule, final_norm=RMSNorm(c.width, c.norm_eps, "final.norm"),
-                        position=None, stream_parts=stream_parts)
+                        position=None, stream_parts=stream_parts, ignorable_tensors=unused)
 
 
 register_architecture(KAKIPEL_ARCHITECTURE, KakipelConfig, build_kakipel, replace=True)
