@@ -60,6 +60,26 @@ def test_model_as_data(tmp_path):
     assert [e.kv.head_dim for e in q.cache_entries()] == [72, 32, 16, 72] and q.stream_parts == []
 
 
+def test_checkpoint_may_carry_norms_of_an_absent_feed_forward(tmp_path):
+    """Tensors that the configuration gives no use - the second pair of norms of a layer without feed-forward - are left
+    alone; any other extra tensor is still an error."""
+    import os
+    from kvcache_b200.engine.loading import load_model
+    from kvcache_b200.weights import SafetensorsFile, WeightError, write_safetensors
+    folder = make_kakipel_folder(tmp_path, "P")
+    path = os.path.join(folder, "model.safetensors")
+    f = SafetensorsFile(path)
+    tensors = {n: f.tensor(n).clone() for n in f.names()}
+    f.close()
+    tensors["l2.norm2"], tensors["l2.norm2b"] = torch.ones(64), torch.ones(64)
+    write_safetensors(path, tensors)
+    assert len(load_model(folder, "float32", "cpu", max_positions=32).schedule) == 5
+    tensors["l2.mlp.gate"] = torch.ones(8, 64)
+    write_safetensors(path, tensors)
+    with pytest.raises(WeightError, match="l2.mlp.gate"):
+        load_model(folder, "float32", "cpu", max_positions=32)
+
+
 def test_cache_holds_one_row_per_token_and_no_values(tmp_path):
     from kvcache_b200.cache import CacheManager
     from kvcache_b200.engine.loading import load_model
