@@ -1,6 +1,7 @@
 """Benchmark of kvcache_b200: decode tokens a second of the Qwen2.5-0.5B shape on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --design kakipel [--sizes 0.5B-like,3B-like]     (another workload, see `run_design`; the default stays as it is)
 
 One JSON line on standard output.  `value`: decoded tokens a second at batch 8 and the
 benchmark context (device-timed decode steps through the engine's step function and device
