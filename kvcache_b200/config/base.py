@@ -96,6 +96,24 @@ class KeyReader:
     def fail(self, message: str) -> None:
         self.problems.append(message)
 
+    def sub(self, key: str, required: bool = True) -> Optional["KeyReader"]:
+        """A reader of the object under `key` (None, with a problem noted if `required`, where there is none)."""
+        value = self.data.get(key)
+        if value is None:
+            if required:
+                self.fail(f"missing key '{key}'")
+            return None
+        if not isinstance(value, Mapping):
+            self.fail(f"'{key}' must be an object")
+            return None
+        return KeyReader(value, f"{self.where}: {key}")
+
+    def absorb(self, child: Optional["KeyReader"]) -> None:
+        """Takes over the problems a reader made by `sub` has found, each under the child's path."""
+        if child is not None:
+            self.problems.extend(f"{child.where.split(': ', 1)[-1]}: {p}" for p in child.problems)
+            child.problems.clear()
+
     def finish(self) -> None:
         if self.problems:
             raise ConfigError(f"{self.where}: " + "; ".join(self.problems))

@@ -7,7 +7,7 @@ paged attention with scale 1/sqrt(D), output projection without bias).
 from __future__ import annotations
 
 import math
-from typing import Dict, Mapping, Optional
+from typing import Dict, Mapping, Optional, Sequence
 
 import torch
 
@@ -16,70 +16,105 @@ from .base import TORCH_DTYPES, LayerContext, Mixer, PagedKVSpec, PositionEncodi
 
 
 class GQAAttention(Mixer):
+    """Options beyond the reference's layer: `value_dim` (values of another size than keys), `qk_norm_eps` (queries and
+    keys divided by their root mean square per head and multiplied by a weight of head_dim numbers that all heads share,
+    `<q name>.norm` / `<k name>.norm`, before the rotation), `head_gate` (a head's result times sigmoid of one number per
+    head, a projection of the mixer's input), `names` (what the q, k, v and output matrices are called after `prefix`)."""
+
     def __init__(self, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int, *, qkv_bias: bool,
                  out_bias: bool, position: Optional[PositionEncoding], window: Optional[int], prefix: str,
-                 dtype: str, scale: Optional[float] = None):
+                 dtype: str, scale: Optional[float] = None, value_dim: Optional[int] = None,
+                 qk_norm_eps: Optional[float] = None, head_gate: Optional[str] = None,
+                 names: Sequence[str] = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight")):
         if num_heads % num_kv_heads != 0:
             raise ValueError(f"num_heads {num_heads} is not a multiple of num_kv_heads {num_kv_heads}")
         if out_bias:
             raise ValueError("an output-projection bias is not supported")
         self.hidden, self.num_heads, self.num_kv_heads, self.head_dim = hidden, num_heads, num_kv_heads, head_dim
+        self.value_dim = head_dim if value_dim is None else int(value_dim)
         self.qkv_bias = qkv_bias
         self.position = position
         self.window = window
         self.prefix = prefix
+        self.names = tuple(names)
+        self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
+        self.head_gate = head_gate
         self.dtype = TORCH_DTYPES[dtype]
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.q_size = num_heads * head_dim
         self.kv_size = num_kv_heads * head_dim
+        self.v_size = num_kv_heads * self.value_dim
+        self.heads_width = num_heads * self.value_dim        # what the output matrix multiplies
+        # The plain layer (equal key and value sizes, no norm of q and k, no gate) has fused and folded forms.
+        self.plain = self.value_dim == head_dim and self.qk_norm_eps is None and head_gate is None
         self.w_qkv: Optional[torch.Tensor] = None
         self.b_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
+        self.q_norm = self.k_norm = None
+
+    def _bias_name(self, i: int) -> str:
+        name = self.names[i]
+        return self.prefix + (name[:-len("weight")] + "bias" if name.endswith("weight") else name + ".b")
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         p = self.prefix
+        q, k, v, o = self.names
         specs = {
-            f"{p}q_proj.weight": TensorSpec((self.q_size, self.hidden)),
-            f"{p}k_proj.weight": TensorSpec((self.kv_size, self.hidden)),
-            f"{p}v_proj.weight": TensorSpec((self.kv_size, self.hidden)),
-            f"{p}o_proj.weight": TensorSpec((self.hidden, self.q_size)),
+            p + q: TensorSpec((self.q_size, self.hidden)),
+            p + k: TensorSpec((self.kv_size, self.hidden)),
+            p + v: TensorSpec((self.v_size, self.hidden)),
+            p + o: TensorSpec((self.hidden, self.heads_width)),
         }
         if self.qkv_bias:
-            specs[f"{p}q_proj.bias"] = TensorSpec((self.q_size,))
-            specs[f"{p}k_proj.bias"] = TensorSpec((self.kv_size,))
-            specs[f"{p}v_proj.bias"] = TensorSpec((self.kv_size,))
+            specs[self._bias_name(0)] = TensorSpec((self.q_size,))
+            specs[self._bias_name(1)] = TensorSpec((self.kv_size,))
+            specs[self._bias_name(2)] = TensorSpec((self.v_size,))
+        if self.qk_norm_eps is not None:
+            specs[p + q + ".norm"] = TensorSpec((self.head_dim,))
+            specs[p + k + ".norm"] = TensorSpec((self.head_dim,))
+        if self.head_gate is not None:
+            specs[p + self.head_gate] = TensorSpec((self.num_heads, self.hidden))
         return specs
+
+    def init_kinds(self) -> Dict[str, str]:
+        if self.qk_norm_eps is None:
+            return {}
+        return {self.prefix + self.names[0] + ".norm": "ones_plus_normal", self.prefix + self.names[1] + ".norm": "ones_plus_normal"}
 
     def bind(self, tensors: Mapping[str, torch.Tensor], device: torch.device) -> None:
         p = self.prefix
-        # One projection for q, k and v: rows [q heads | k heads | v heads].
-        self.w_qkv = torch.cat([tensors[f"{p}{n}_proj.weight"] for n in "qkv"], dim=0).to(self.dtype).to(device).contiguous()
+        # One projection for q, k and v (and the heads' gates): rows [q heads | k heads | v heads | gates].
+        rows = [tensors[p + n] for n in self.names[:3]]
+        if self.head_gate is not None:
+            rows.append(tensors[p + self.head_gate])
+        self.w_qkv = torch.cat(rows, dim=0).to(self.dtype).to(device).contiguous()
         if self.qkv_bias:
-            self.b_qkv = torch.cat([tensors[f"{p}{n}_proj.bias"] for n in "qkv"], dim=0).to(torch.float32).to(device).contiguous()
-        self.w_o = tensors[f"{p}o_proj.weight"].to(self.dtype).to(device).contiguous()
+            bias = [tensors[self._bias_name(i)] for i in range(3)]
+            if self.head_gate is not None:
+                bias.append(torch.zeros(self.num_heads))
+            self.b_qkv = torch.cat(bias, dim=0).to(torch.float32).to(device).contiguous()
+        self.w_o = tensors[p + self.names[3]].to(self.dtype).to(device).contiguous()
+        if self.qk_norm_eps is not None:
+            self.q_norm = tensors[p + self.names[0] + ".norm"].to(torch.float32).to(device).contiguous()
+            self.k_norm = tensors[p + self.names[1] + ".norm"].to(torch.float32).to(device).contiguous()
+        if self.position is not None:
+            self.position.bind(tensors, device)
         # The folded projection of decode steps rotates inside the product and wants a second copy of the q/k/v weight
         # with each head's rows reordered (made when first asked for): possible in bfloat16, with whole-head rotation (or
         # none) and heads in steps of 16.
         self.w_qkv_paired = self.b_qkv_paired = None
-        self._can_pair = self.dtype == torch.bfloat16 and self.head_dim % 16 == 0 and device.type == "cuda"
-
-    def _pair_rows(self, kernels) -> bool:
-        """Makes the row-paired copy of the q/k/v weight and bias if the kernel set can use one."""
-        rotation = self.position.rotation() if self.position is not None else None
-        whole = rotation is None or rotation.cos.shape[1] * 2 == self.head_dim
-        if self.w_qkv_paired is None and self._can_pair and whole and hasattr(kernels, "pair_rotation_rows"):
-            order = kernels.pair_rotation_rows(self.num_heads + 2 * self.num_kv_heads, self.head_dim).to(self.w_qkv.device)
-            self.w_qkv_paired = self.w_qkv.index_select(0, order).contiguous()
-            if self.b_qkv is not None:
-                self.b_qkv_paired = self.b_qkv.index_select(0, order).contiguous()
-        return self.w_qkv_paired is not None
+        self._can_pair = self.plain and self.dtype == torch.bfloat16 and self.head_dim % 16 == 0 and device.type == "cuda"
 
     def weight_bytes(self) -> int:
         n = self.w_qkv.numel() * self.w_qkv.element_size() + self.w_o.numel() * self.w_o.element_size()
         return n + (self.b_qkv.numel() * 4 if self.b_qkv is not None else 0)
 
+    def out_weight(self) -> torch.Tensor:
+        return self.w_o
+
     def cache_spec(self) -> PagedKVSpec:
-        return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window)
+        return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window,
+                           None if self.value_dim == self.head_dim else self.value_dim)
 
     def step_planners(self, kernels):
         planner = getattr(kernels, "paged_attention_planner", None)
@@ -87,7 +122,7 @@ class GQAAttention(Mixer):
 
     def supports_fold(self, norm, kernels, num_rows: int) -> bool:
         can = getattr(kernels, "can_fold", None)
-        return (can is not None and norm.fold_params() is not None
+        return (self.plain and can is not None and norm.fold_params() is not None
                 and can(self.dtype, num_rows, self.hidden, self.q_size + 2 * self.kv_size)
                 and can(self.dtype, num_rows, self.q_size, self.hidden) and self._pair_rows(kernels))
 
@@ -105,9 +140,34 @@ class GQAAttention(Mixer):
         k.linear_into_residual(attn, self.w_o, h, h16)
 
 
+    def forward_heads(self, x: torch.Tensor, ctx: LayerContext, out: torch.Tensor, out_col: int = 0, scale: float = 1.0) -> None:
+        """The heads' results, gated and times `scale`, into columns out_col .. out_col + heads_width of `out` (what the
+        output matrix multiplies): the form a mixer that runs beside another one is asked for."""
+        T = x.shape[0]
+        k, ws = ctx.kernels, ctx.workspace
+        qkv = ws.buffer("attn.qkv", (T, self.w_qkv.shape[0]), self.dtype)
+        k.linear(x, self.w_qkv, qkv)
+        rotation = self.position.rotation() if self.position is not None else None
+        cos, sin = (rotation.cos, rotation.sin) if rotation else (None, None)
+        q = ws.buffer("attn.q", (T, self.q_size), self.dtype)
+        k.qkv_rope_append(qkv, self.b_qkv, cos, sin, ctx.batch, ctx.kv, q, self.num_heads, q_norm=self.q_norm, k_norm=self.k_norm,
+                          norm_eps=self.qk_norm_eps or 0.0)
+        direct = self.head_gate is None and scale == 1.0 and out_col == 0 and out.shape[1] == self.heads_width
+        attn = out if direct else ws.buffer("attn.out", (T, self.heads_width), self.dtype)
+        k.paged_attention(q, ctx.batch, ctx.kv, attn, self.num_heads, self.scale, ws)
+        if not direct:
+            gate = (qkv, self.q_size + self.kv_size + self.v_size) if self.head_gate is not None else None
+            k.head_gate(attn, gate, self.num_heads, self.value_dim, scale, out, out_col)
+
     def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
         T = x.shape[0]
         k, ws = ctx.kernels, ctx.workspace
+        delta = ws.buffer("attn.delta", (T, self.hidden), self.dtype)
+        if not self.plain:
+            gated = ws.buffer("attn.gated", (T, self.heads_width), self.dtype)
+            self.forward_heads(x, ctx, gated)
+            k.linear(gated, self.w_o, delta)
+            return delta
         qkv = ws.buffer("attn.qkv", (T, self.q_size + 2 * self.kv_size), self.dtype)
         k.linear(x, self.w_qkv, qkv)
         rotation = self.position.rotation() if self.position is not None else None
@@ -119,6 +179,5 @@ class GQAAttention(Mixer):
             q = ws.buffer("attn.q", (T, self.q_size), self.dtype)
             k.qkv_rope_append(qkv, self.b_qkv, cos, sin, ctx.batch, ctx.kv, q, self.num_heads)
             k.paged_attention(q, ctx.batch, ctx.kv, attn, self.num_heads, self.scale, ws)
-        delta = ws.buffer("attn.delta", (T, self.hidden), self.dtype)
         k.linear(attn, self.w_o, delta)
         return delta

@@ -14,6 +14,7 @@ It declares the checkpoint tensors it wants (`tensor_specs`), takes them
                       and the work lists its kernels want with `step_planners()`.
 * `FeedForward`     - `forward(x, ctx) -> delta`.
 * `Block`           - the arrangement of the four in one layer.
+* `StreamPart`      - acts on the residual stream between layers; `EmbeddingPart` on the embedded rows.
 """
 from __future__ import annotations
 
@@ -24,7 +25,7 @@ import torch
 
 from ..weights.loader import TensorSpec
 
-TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "int32": torch.int32}
 
 
 @dataclass(frozen=True)
@@ -235,6 +236,18 @@ class StreamPart(Part):
     needs_embedding = False
 
     def forward(self, h: torch.Tensor, pending, ctx: LayerContext, argument: int):
+        raise NotImplementedError
+
+
+class EmbeddingPart(Part):
+    """Acts on the embedded rows before the first layer, with per-request state of its own if it asks for some
+    (`state_spec`, as a mixer's: `[slots, *shape]`, zeroed at admission, handed over as `ctx.state`).  The step's
+    token ids are `ctx.batch.token_ids` or, where `ctx.batch.token_src[r] >= 0`, `ctx.batch.last_tokens[token_src[r]]`."""
+
+    def state_spec(self):
+        return None
+
+    def forward(self, h: torch.Tensor, ctx: LayerContext) -> None:
         raise NotImplementedError
 
 

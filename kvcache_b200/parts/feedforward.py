@@ -9,21 +9,29 @@ from ..weights.loader import TensorSpec
 from .base import TORCH_DTYPES, FeedForward, LayerContext
 
 
+GATED_ACTIVATIONS = ("silu", "clamped_swiglu")
+
+
 class GatedMLP(FeedForward):
-    """delta = (act(x Wg^T) * (x Wu^T)) Wd^T with act = silu; no biases."""
+    """delta = act(x Wg^T, x Wu^T) Wd^T; no biases.  act is "silu": silu(g) * u, or "clamped_swiglu":
+    g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit) and u' = clamp(u, -limit, limit)."""
 
     def __init__(self, hidden: int, intermediate: int, *, activation: str, prefix: str, dtype: str,
-                 names: Sequence[str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
+                 names: Sequence[str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight"), limit: float = 0.0):
         """`names`: what the gate, up and down matrices are called after `prefix` in the checkpoint."""
         self.names = tuple(names)
-        if activation != "silu":
+        if activation not in GATED_ACTIVATIONS:
             raise ValueError(f"activation '{activation}' is not supported by the gated feed-forward kernel")
+        if activation == "clamped_swiglu" and not limit > 0.0:
+            raise ValueError("the clamped activation needs a positive limit")
+        self.activation, self.limit = activation, float(limit)
         self.hidden, self.intermediate = hidden, intermediate
         self.prefix = prefix
         self.dtype = TORCH_DTYPES[dtype]
         self.w_gate_up: Optional[torch.Tensor] = None
         self.w_down: Optional[torch.Tensor] = None
         self.interleaved = False
+        self.delta_name = "ffn.delta"          # the workspace buffer of the result (another name where two run in one layer)
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         p = self.prefix
@@ -53,7 +61,7 @@ class GatedMLP(FeedForward):
 
     def supports_fold(self, norm, kernels, num_rows: int) -> bool:
         can = getattr(kernels, "can_fold", None)
-        return (can is not None and self.interleaved and norm.fold_params() is not None
+        return (can is not None and self.interleaved and self.activation == "silu" and norm.fold_params() is not None
                 and can(self.dtype, num_rows, self.hidden, 2 * self.intermediate)
                 and can(self.dtype, num_rows, self.intermediate, self.hidden))
 
@@ -70,30 +78,55 @@ class GatedMLP(FeedForward):
         T = x.shape[0]
         k, ws = ctx.kernels, ctx.workspace
         act = ws.buffer("ffn.act", (T, self.intermediate), self.dtype)
-        k.gate_up_act(x, self.w_gate_up, act, ws, self.interleaved)
-        delta = ws.buffer("ffn.delta", (T, self.hidden), self.dtype)
+        if self.activation == "silu":
+            k.gate_up_act(x, self.w_gate_up, act, ws, self.interleaved)
+        else:
+            k.gate_up_act(x, self.w_gate_up, act, ws, self.interleaved, activation=self.activation, limit=self.limit)
+        delta = ws.buffer(self.delta_name, (T, self.hidden), self.dtype)
         k.linear(act, self.w_down, delta)
         return delta
 
 
-class RoutedMLP(FeedForward):
-    """A mixture of small feed-forwards: delta = sum over the `top` experts e with the largest router logits of
-    w_e * Wdown_e act(Wup_e x), the weights w being the softmax over the chosen logits only; no biases.
+ROUTED_ACTIVATIONS = ("relu2", "clamped_swiglu")
 
-    The router's logits are float32 (from the rows in the compute type).  The experts' matrices are stacked
-    ([experts, ff, hidden] and [experts, hidden, ff]) so that one grouped product serves all of them; which rows go to
-    which expert is decided on the device, and the launches do not depend on it.
+
+class RoutedMLP(FeedForward):
+    """A mixture of small feed-forwards: delta = sum over the `top` chosen experts e of w_e * expert_e(x) (+ shared(x));
+    no biases.  The router's logits are float32 (from the rows in the compute type).
+
+    `scores`: "chosen" - the experts with the largest logits, weights = softmax over the chosen logits only;
+    "all" - weights = the softmax over all experts' logits at the chosen ones, as they are (they do not sum to 1).
+    `activation`: "relu2" - expert(x) = Wdown relu(Wup x)^2 (`expert_names` = up, down); "clamped_swiglu" - expert(x) =
+    Wdown (g sigmoid(1.702 g) (u + 1)) with g = min(Wgate x, limit), u = clamp(Wup x, -limit, limit) (`expert_names` =
+    gate, up, down).  `shared`: a feed-forward that every row takes, added to the routed sum.
+
+    The experts' matrices are stacked ([experts, ff, hidden] - gate and up rows in turn, [experts, 2 ff, hidden], for the
+    gated form - and [experts, hidden, ff]) so that one grouped product serves all of them; which rows go to which expert
+    is decided on the device, and the launches do not depend on it.
     """
 
     def __init__(self, hidden: int, expert_ff: int, experts: int, top: int, *, activation: str, prefix: str, dtype: str,
-                 router_name: str = "router", expert_names: Sequence[str] = ("e{e}.up", "e{e}.down")):
-        if activation != "relu2":
+                 router_name: str = "router", expert_names: Optional[Sequence[str]] = None, scores: str = "chosen",
+                 limit: float = 0.0, shared: Optional[FeedForward] = None):
+        if activation not in ROUTED_ACTIVATIONS:
             raise ValueError(f"activation '{activation}' is not supported by the routed feed-forward kernels")
         if not 1 <= top <= experts:
             raise ValueError(f"top {top} of {experts} experts")
+        if scores not in ("chosen", "all"):
+            raise ValueError(f"scores '{scores}' (chosen, all)")
+        if activation == "clamped_swiglu" and not limit > 0.0:
+            raise ValueError("the clamped activation needs a positive limit")
         self.hidden, self.expert_ff, self.experts, self.top = hidden, expert_ff, experts, top
-        self.activation = activation
+        self.activation, self.scores, self.limit = activation, scores, float(limit)
+        self.gated = activation == "clamped_swiglu"
+        if expert_names is None:
+            expert_names = ("e{e}.gate", "e{e}.up", "e{e}.down") if self.gated else ("e{e}.up", "e{e}.down")
+        if len(expert_names) != (3 if self.gated else 2):
+            raise ValueError(f"{len(expert_names)} expert matrix names for activation '{activation}'")
         self.prefix, self.router_name, self.expert_names = prefix, router_name, tuple(expert_names)
+        self.shared = shared
+        if shared is not None and hasattr(shared, "delta_name"):
+            shared.delta_name = "ffn.shared_delta"
         self.dtype = TORCH_DTYPES[dtype]
         self.w_router: Optional[torch.Tensor] = None
         self.w_up: Optional[torch.Tensor] = None
@@ -105,28 +138,50 @@ class RoutedMLP(FeedForward):
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         specs = {self.prefix + self.router_name: TensorSpec((self.experts, self.hidden))}
         for e in range(self.experts):
-            specs[self._expert(0, e)] = TensorSpec((self.expert_ff, self.hidden))
-            specs[self._expert(1, e)] = TensorSpec((self.hidden, self.expert_ff))
+            for which in range(len(self.expert_names) - 1):
+                specs[self._expert(which, e)] = TensorSpec((self.expert_ff, self.hidden))
+            specs[self._expert(len(self.expert_names) - 1, e)] = TensorSpec((self.hidden, self.expert_ff))
+        if self.shared is not None:
+            specs.update(self.shared.tensor_specs())
         return specs
 
+    def init_kinds(self) -> Dict[str, str]:
+        return self.shared.init_kinds() if self.shared is not None else {}
+
     def bind(self, tensors: Mapping[str, torch.Tensor], device: torch.device) -> None:
-        self.w_router = tensors[self.prefix + self.router_name].to(self.dtype).to(device).contiguous()
-        self.w_up = torch.stack([tensors[self._expert(0, e)] for e in range(self.experts)]).to(self.dtype).to(device).contiguous()
-        self.w_down = torch.stack([tensors[self._expert(1, e)] for e in range(self.experts)]).to(self.dtype).to(device).contiguous()
+        place = lambda t: t.to(self.dtype).to(device).contiguous()
+        E = range(self.experts)
+        self.w_router = place(tensors[self.prefix + self.router_name])
+        if self.gated:
+            # Row 2 i is gate row i, row 2 i + 1 up row i: a product's thread holds both numbers of an index.
+            self.w_up = place(torch.stack([torch.stack([tensors[self._expert(0, e)], tensors[self._expert(1, e)]], dim=1)
+                                           .reshape(2 * self.expert_ff, self.hidden) for e in E]))
+        else:
+            self.w_up = place(torch.stack([tensors[self._expert(0, e)] for e in E]))
+        self.w_down = place(torch.stack([tensors[self._expert(len(self.expert_names) - 1, e)] for e in E]))
+        if self.shared is not None:
+            self.shared.bind(tensors, device)
 
     def weight_bytes(self) -> int:
         """Bytes one row reads: the router and its `top` experts (a step of many rows reads up to all experts)."""
         size = self.w_up.element_size()
-        return (self.w_router.numel() + self.top * 2 * self.expert_ff * self.hidden) * size
+        per_expert = (3 if self.gated else 2) * self.expert_ff * self.hidden
+        shared = self.shared.weight_bytes() if self.shared is not None else 0
+        return (self.w_router.numel() + self.top * per_expert) * size + shared
 
     def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
         T = x.shape[0]
         k, ws = ctx.kernels, ctx.workspace
+        base = self.shared.forward(x, ctx) if self.shared is not None else None
         logits = ws.buffer("moe.logits", (T, self.experts), torch.float32)
         k.linear(x, self.w_router, logits)
         chosen = ws.buffer("moe.chosen", (T, self.top), torch.int32)
         share = ws.buffer("moe.share", (T, self.top), torch.float32)
-        k.route_top(logits, chosen, share)
         delta = ws.buffer("ffn.delta", (T, self.hidden), self.dtype)
-        k.routed_experts(x, self.w_up, self.w_down, chosen, share, delta, self.activation, ws)
+        if self.scores == "chosen" and not self.gated and base is None:
+            k.route_top(logits, chosen, share)
+            k.routed_experts(x, self.w_up, self.w_down, chosen, share, delta, self.activation, ws)
+        else:
+            k.route_top(logits, chosen, share, scores=self.scores)
+            k.routed_experts(x, self.w_up, self.w_down, chosen, share, delta, self.activation, ws, limit=self.limit, base=base)
         return delta

@@ -38,7 +38,7 @@ class DecoderModel:
     def __init__(self, *, config: Any, dtype: str, vocab_size: int, width: int, embed_name: str,
                  head_name: Optional[str], blocks: Sequence[Block], schedule: Sequence[LayerCall],
                  final_norm: Norm, position: Optional[PositionEncoding] = None, ignorable_tensors: Sequence[str] = (),
-                 stream_parts: Sequence[Any] = ()):
+                 stream_parts: Sequence[Any] = (), embedding_parts: Sequence[Any] = ()):
         self.config = config
         self.dtype_name = dtype
         self.dtype = TORCH_DTYPES[dtype]
@@ -49,6 +49,8 @@ class DecoderModel:
         self.final_norm = final_norm
         self.position = position
         self.stream_parts = list(stream_parts)
+        # Parts that act on the embedded rows (see `EmbeddingPart`); each one's state is a cache entry after the layers'.
+        self.embedding_parts = list(embedding_parts)
         self.keeps_embedding = any(getattr(part, "needs_embedding", False) for part in self.stream_parts)
         # Names (shell patterns) of tensors that checkpoints of this architecture may carry without the model using them.
         self.ignorable_tensors = tuple(ignorable_tensors)
@@ -80,7 +82,7 @@ class DecoderModel:
         return self.head_name is None
 
     def _parts(self):
-        out = list(self.blocks) + [self.final_norm] + list(self.stream_parts)
+        out = list(self.blocks) + [self.final_norm] + list(self.stream_parts) + list(self.embedding_parts)
         if self.position is not None:
             out.append(self.position)
         return out
@@ -123,6 +125,8 @@ class DecoderModel:
         for cache_id in range(len(self._writers)):
             mixer = self.blocks[self._writers[cache_id]].mixer
             entries.append(CacheEntry(mixer.cache_spec(), mixer.state_spec()))
+        for part in self.embedding_parts:
+            entries.append(CacheEntry(None, part.state_spec()))
         return entries
 
     def step_planners(self, kernels: Any) -> List[Any]:
@@ -138,7 +142,7 @@ class DecoderModel:
         may change the embedded rows behind the back of their rounded copy."""
         if self.position is not None and type(self.position).on_embed is not PositionEncoding.on_embed:
             return False
-        if self.stream_parts:
+        if self.stream_parts or self.embedding_parts:
             return False
         key = (id(kernels), num_rows, getattr(kernels, "fold_key", None))
         found = self._fold_cache.get(key)
@@ -169,6 +173,9 @@ class DecoderModel:
         base = LayerContext(batch=batch, kernels=kernels, workspace=workspace, embedded=embedded)
         if self.position is not None:
             self.position.on_embed(h, base)
+        for i, part in enumerate(self.embedding_parts):
+            part.forward(h, LayerContext(batch=batch, kernels=kernels, workspace=workspace,
+                                         state=cache.state(len(self._writers) + i), embedded=embedded))
         pending = None
         for index, call in enumerate(self.schedule):
             ctx = LayerContext(batch=batch, kernels=kernels, workspace=workspace,

@@ -44,3 +44,16 @@ class RMSNorm(Norm):
 
     def fold_params(self):
         return self.weight, self.eps
+
+
+class PassNorm(Norm):
+    """No normalisation: adds the pending delta (normalised by its own norm if it is a `NormedDelta`) and hands the
+    rows on as they are, rounded to the compute type - the place of a norm in a block whose sublayers read the
+    residual stream itself."""
+
+    def add_norm(self, h, delta, out, ctx: LayerContext, rows=None, tail=None) -> None:
+        post = delta.post.fold_params() if isinstance(delta, NormedDelta) else None
+        if isinstance(delta, NormedDelta) and post is None:
+            raise ValueError("a delta can be normalised before the add only by a norm of the form v * rsqrt(mean(v^2) + eps) * w")
+        d = delta.delta if isinstance(delta, NormedDelta) else delta
+        ctx.kernels.norm_add_rmsnorm(h, d, post[0] if post else None, post[1] if post else 0.0, None, 0.0, out, rows, tail)

@@ -38,6 +38,28 @@ class RampScaling:
         return 0.1 * math.log(self.factor) + 1.0
 
 
+class WavelengthScaling:
+    """Slows the pairs of a rotation by their wavelength l = 2 pi / f against the `original` context: pairs with
+    l < original / high keep f, pairs with l > original / low turn at f / factor, and between the two the frequency is
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low).  cos and sin keep their size."""
+
+    def __init__(self, factor: float, low: float, high: float, original: float):
+        self.factor, self.low, self.high, self.original = float(factor), float(low), float(high), float(original)
+
+    def key(self) -> tuple:
+        return (self.factor, self.low, self.high, self.original)
+
+    def blend(self, freq: np.ndarray, dims: int, base: float) -> np.ndarray:
+        wavelength = 2.0 * math.pi / freq
+        s = (self.original / wavelength - self.low) / (self.high - self.low)
+        mixed = (1.0 - s) * freq / self.factor + s * freq
+        return np.where(wavelength < self.original / self.high, freq,
+                        np.where(wavelength > self.original / self.low, freq / self.factor, mixed))
+
+    def gain(self) -> float:
+        return 1.0
+
+
 class RotaryHalf(PositionEncoding):
     """Pairs dimension t with t + rotary_dim/2; angle = pos * theta^(-2t / rotary_dim).
 
@@ -46,7 +68,9 @@ class RotaryHalf(PositionEncoding):
     position carries no accumulated float32 error.
     """
 
-    def __init__(self, rotary_dim: int, theta: float, max_positions: int, scaling: Optional["RampScaling"] = None):
+    def __init__(self, rotary_dim: int, theta: float, max_positions: int, scaling=None):
+        """`scaling`: None, or an object with `blend(freq, dims, base) -> freq` and `gain()` (`RampScaling`,
+        `WavelengthScaling`)."""
         if rotary_dim % 2 != 0 or rotary_dim < 2:
             raise ValueError(f"rotary_dim must be even and positive, got {rotary_dim}")
         self.rotary_dim = rotary_dim

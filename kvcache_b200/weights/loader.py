@@ -46,7 +46,7 @@ class WeightError(ValueError):
 @dataclass(frozen=True)
 class TensorSpec:
     """What a part expects of one checkpoint tensor."""
-    shape: Tuple[int, ...]
+    shape: Tuple[Optional[int], ...]   # None: a size that the checkpoint decides (the part checks it when it binds)
     kind: str = FLOAT          # FLOAT or INTEGER
     optional: bool = False     # an absent optional tensor is not an error (a tied output matrix)
 
@@ -101,7 +101,8 @@ def load_tensors(folder: str, specs: Mapping[str, TensorSpec], *, strict: bool =
         if name not in where:
             continue
         f = where[name]
-        if tuple(f.shape(name)) != tuple(spec.shape):
+        found = tuple(f.shape(name))
+        if len(found) != len(spec.shape) or any(e is not None and e != g for e, g in zip(spec.shape, found)):
             wrong_shape.append((name, tuple(spec.shape), tuple(f.shape(name))))
         is_float = f.dtype(name).is_floating_point
         if is_float != (spec.kind == FLOAT):

@@ -39,6 +39,8 @@ def random_tensors(specs: Mapping[str, TensorSpec], seed: int, std: float,
             continue
         if spec.kind != FLOAT:
             raise ValueError(f"no random initialisation for integer tensor '{name}'")
+        if any(n is None for n in spec.shape):
+            raise ValueError(f"tensor '{name}' has a size that only a checkpoint decides; the configuration must state it for random weights")
         values = torch.randn(spec.shape, generator=_generator(seed, name), dtype=torch.float32) * std
         if kind == "ones_plus_normal":
             values = values + 1.0

@@ -48,13 +48,15 @@ class TorchKernels:
             y = y + bias.to(self.f)
         out.copy_(y.to(out.dtype))
 
-    def qkv_rope_append(self, qkv, bias, cos, sin, batch, kv, q_out, num_heads):
+    def qkv_rope_append(self, qkv, bias, cos, sin, batch, kv, q_out, num_heads, q_norm=None, k_norm=None, norm_eps=0.0):
         f = self.f
         T = qkv.shape[0]
         Hq, Hkv, D = num_heads, kv.spec.num_kv_heads, kv.spec.head_dim
         x = qkv.to(f)
         if bias is not None:
             x = x + bias.to(f)
+        if q_norm is not None or kv.spec.v_head_dim != D or x.shape[1] != (Hq + 2 * Hkv) * D:
+            return self._qkv_norm_rope_append(x, cos, sin, batch, kv, q_out, Hq, q_norm, k_norm, norm_eps)
         x = x.view(T, Hq + 2 * Hkv, D).clone()
         pos = batch.positions.long()
         if cos is not None:
@@ -73,6 +75,31 @@ class TorchKernels:
             kv.k_pages[page, :, slot, :] = x[:, Hq:Hq + Hkv, :].to(kv.k_pages.dtype)
             kv.v_pages[page, :, slot, :] = x[:, Hq + Hkv:, :].to(kv.v_pages.dtype)
 
+    def _qkv_norm_rope_append(self, x, cos, sin, batch, kv, q_out, Hq, q_norm, k_norm, eps):
+        """Rows [q heads of D | k heads of D | v heads of Dv | columns that are not this operator's]."""
+        f = self.f
+        T = x.shape[0]
+        Hkv, D, Dv = kv.spec.num_kv_heads, kv.spec.head_dim, kv.spec.v_head_dim
+        q = x[:, :Hq * D].reshape(T, Hq, D).clone()
+        k = x[:, Hq * D:(Hq + Hkv) * D].reshape(T, Hkv, D).clone()
+        v = x[:, (Hq + Hkv) * D:(Hq + Hkv) * D + Hkv * Dv].reshape(T, Hkv, Dv)
+        if q_norm is not None:
+            q = q * torch.rsqrt((q * q).mean(dim=-1, keepdim=True) + eps) * q_norm.to(f)
+            k = k * torch.rsqrt((k * k).mean(dim=-1, keepdim=True) + eps) * k_norm.to(f)
+        pos = batch.positions.long()
+        if cos is not None:
+            half = cos.shape[1]
+            c, s = cos[pos].to(f)[:, None, :], sin[pos].to(f)[:, None, :]
+            for t in (q, k):
+                u, w = t[..., :half].clone(), t[..., half:2 * half].clone()
+                t[..., :half], t[..., half:2 * half] = u * c - w * s, w * c + u * s
+        q_out.copy_(q.reshape(T, Hq * D).to(q_out.dtype))
+        if kv.writes:
+            page = kv.block_table[batch.row_segment.long(), pos // kv.page_size].long()
+            assert bool((page >= 0).all()), "append into a page the block table does not hold"
+            kv.k_pages[page, :, pos % kv.page_size, :] = k.to(kv.k_pages.dtype)
+            kv.v_pages[page, :, pos % kv.page_size, :] = v.to(kv.v_pages.dtype)
+
     def paged_attention(self, q, batch, kv, out, num_heads, scale, workspace=None):
         f = self.f
         T = q.shape[0]
@@ -80,7 +107,7 @@ class TorchKernels:
         group = Hq // Hkv
         window = kv.spec.window
         qf = q.to(f).view(T, Hq, D)
-        result = torch.zeros(T, Hq, D, dtype=f, device=q.device)
+        result = torch.zeros(T, Hq, kv.spec.v_head_dim, dtype=f, device=q.device)
         for r in range(T):
             p = int(batch.positions[r])
             seg = int(batch.row_segment[r])
@@ -93,21 +120,29 @@ class TorchKernels:
             for h in range(Hq):
                 s = (keys[:, h // group, :] @ qf[r, h]) * scale
                 result[r, h] = torch.softmax(s, dim=0) @ vals[:, h // group, :]
-        out.copy_(result.view(T, Hq * D).to(out.dtype))
+        out.copy_(result.view(T, -1).to(out.dtype))
 
-    def silu_mul(self, gate_up, out, interleaved=False):
+    @staticmethod
+    def _gated(g, u, activation, limit):
+        if activation == "silu":
+            return g / (1.0 + torch.exp(-g)) * u
+        assert activation == "clamped_swiglu"
+        g, u = torch.clamp(g, max=limit), torch.clamp(u, min=-limit, max=limit)
+        return g * torch.sigmoid(1.702 * g) * (u + 1.0)
+
+    def silu_mul(self, gate_up, out, interleaved=False, activation="silu", limit=0.0):
         I = out.shape[1]
         if interleaved:
             pairs = gate_up.view(gate_up.shape[0], I // 8, 2, 8)
             g, u = pairs[:, :, 0, :].reshape(-1, I).to(self.f), pairs[:, :, 1, :].reshape(-1, I).to(self.f)
         else:
             g, u = gate_up[:, :I].to(self.f), gate_up[:, I:].to(self.f)
-        out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
+        out.copy_(self._gated(g, u, activation, limit).to(out.dtype))
 
-    def gate_up_act(self, x, w_gate_up, out, workspace, interleaved):
+    def gate_up_act(self, x, w_gate_up, out, workspace, interleaved, activation="silu", limit=0.0):
         gate_up = torch.empty(x.shape[0], w_gate_up.shape[0], dtype=out.dtype, device=out.device)
         self.linear(x, w_gate_up, gate_up)
-        self.silu_mul(gate_up, out, interleaved)
+        self.silu_mul(gate_up, out, interleaved, activation, limit)
 
     def sample_parts(self, vocab):
         return 1
@@ -197,18 +232,99 @@ class TorchKernels:
             result[r] = weights @ keys[:, :value_dim]
         out.copy_(result.view(T, num_heads * value_dim).to(out.dtype))
 
-    def route_top(self, logits, chosen, share):
-        best, which = torch.topk(logits.to(self.f), chosen.shape[1], dim=-1)
+    def route_top(self, logits, chosen, share, scores="chosen"):
+        z = logits.to(self.f)
+        best, which = torch.topk(z, chosen.shape[1], dim=-1)
         chosen.copy_(which.to(torch.int32))
-        share.copy_(torch.softmax(best, dim=-1).to(torch.float32))
+        if scores == "all":
+            share.copy_(torch.gather(torch.softmax(z, dim=-1), 1, which).to(torch.float32))
+        else:
+            share.copy_(torch.softmax(best, dim=-1).to(torch.float32))
 
-    def routed_experts(self, x, w_up, w_down, chosen, share, out, activation, workspace=None):
-        assert activation == "relu2"
+    def routed_experts(self, x, w_up, w_down, chosen, share, out, activation, workspace=None, limit=0.0, base=None):
         f = self.f
-        result = torch.zeros(x.shape[0], w_down.shape[1], dtype=f)
+        result = torch.zeros(x.shape[0], w_down.shape[1], dtype=f) if base is None else base.to(f).clone()
         for r in range(x.shape[0]):
             for s in range(chosen.shape[1]):
                 e = int(chosen[r, s])
-                a = torch.relu(w_up[e].to(f) @ x[r].to(f)) ** 2
+                up = w_up[e].to(f) @ x[r].to(f)
+                if activation == "relu2":
+                    a = torch.relu(up) ** 2
+                else:
+                    a = self._gated(up[0::2], up[1::2], activation, limit)     # gate and up rows in turn
                 result[r] += share[r, s].to(f) * (w_down[e].to(f) @ a.to(x.dtype).to(f))
         out.copy_(result.to(out.dtype))
+
+    # ---- operators of the hashed pair embedding, gated heads and the matrix-state mixers ----------------------------
+    def bigram_embed(self, table, batch, previous, h, buckets, mul_prev, mul_cur, vocab):
+        ids = batch.token_ids.long()
+        if batch.token_src is not None:
+            ids = torch.where(batch.token_src >= 0, batch.last_tokens[batch.token_src.clamp(min=0).long()].long(), ids)
+        for s in range(batch.num_segments):
+            lo, n, slot = int(batch.seg_q_start[s]), int(batch.seg_q_len[s]), int(batch.seg_slot[s])
+            for r in range(lo, lo + n):
+                if int(batch.positions[r]) == 0:
+                    row = buckets
+                else:
+                    before = int(ids[r - 1]) if r > lo else int(previous[slot])
+                    row = (before * mul_prev + int(ids[r]) * mul_cur) % buckets
+                h[r] += table[row].to(torch.float32)
+            previous[slot] = int(ids[lo + n - 1])
+
+    def head_gate(self, x, gate, num_heads, value_dim, scale, out, out_col=0):
+        f = self.f
+        T = x.shape[0]
+        y = x.to(f).view(T, num_heads, value_dim)
+        if gate is not None:
+            src, col = gate
+            y = y * torch.sigmoid(src[:, col:col + num_heads].to(f))[:, :, None]
+        out[:, out_col:out_col + num_heads * value_dim] = (y * scale).reshape(T, -1).to(out.dtype)
+
+    def head_norm_gate(self, o, weight, eps, gate, activation, scale, out, out_col, num_heads, value_dim):
+        f = self.f
+        T = o.shape[0]
+        y = o.to(f).view(T, num_heads, value_dim)
+        y = y * torch.rsqrt((y * y).mean(dim=-1, keepdim=True) + eps)
+        y = y * (weight.to(f).view(num_heads, value_dim) if weight.numel() == num_heads * value_dim else weight.to(f))
+        src, col = gate
+        g = src[:, col:col + num_heads * value_dim].to(f)
+        g = g * torch.sigmoid(g) if activation == "silu" else torch.sigmoid(g)
+        out[:, out_col:out_col + num_heads * value_dim] = (y.reshape(T, -1) * g * scale).to(out.dtype)
+
+    def _segments(self, batch):
+        for s in range(batch.num_segments):
+            yield int(batch.seg_q_start[s]), int(batch.seg_q_len[s]), int(batch.seg_slot[s])
+
+    def gated_linear_scan(self, proj, cols, z, tau, q_scale, batch, memory, out, H, D, Dv):
+        f = self.f
+        qc, kc, vc = cols
+        for lo, n, slot in self._segments(batch):
+            S = memory[slot].to(f)                                   # [H, Dv, D]
+            for r in range(lo, lo + n):
+                q = proj[r, qc:qc + H * D].to(f).view(H, D) * q_scale
+                k = proj[r, kc:kc + H * D].to(f).view(H, D)
+                v = proj[r, vc:vc + H * Dv].to(f).view(H, Dv)
+                decay = torch.exp(torch.nn.functional.logsigmoid(z[r].to(f)).view(H, D) / tau)
+                S = decay[:, None, :] * S + v[:, :, None] * k[:, None, :]
+                out[r] = torch.einsum("hvd,hd->hv", S, q).reshape(-1).to(out.dtype)
+            memory[slot] = S.to(memory.dtype)
+
+    def matrix_memory_scan(self, proj, cols, cap, q_scale, floor, batch, memory, normalizer, maximum, out, H, D, Dv):
+        f = self.f
+        qc, kc, vc, ic, fc = cols
+        for lo, n, slot in self._segments(batch):
+            S, nz, m = memory[slot].to(f), normalizer[slot].to(f), maximum[slot].to(f)
+            for r in range(lo, lo + n):
+                q = proj[r, qc:qc + H * D].to(f).view(H, D) * q_scale
+                k = proj[r, kc:kc + H * D].to(f).view(H, D)
+                v = proj[r, vc:vc + H * Dv].to(f).view(H, Dv)
+                gi = cap * torch.tanh(proj[r, ic:ic + H].to(f) / cap)
+                gf = torch.nn.functional.logsigmoid(cap * torch.tanh(proj[r, fc:fc + H].to(f) / cap))
+                m_new = torch.maximum(gf + m, gi)
+                keep, take = torch.exp(gf + m - m_new), torch.exp(gi - m_new)
+                S = keep[:, None, None] * S + take[:, None, None] * v[:, :, None] * k[:, None, :]
+                nz = keep[:, None] * nz + take[:, None] * k
+                m = m_new
+                denom = torch.maximum((nz * q).sum(dim=-1).abs(), torch.exp(-m)) + floor
+                out[r] = (torch.einsum("hvd,hd->hv", S, q) / denom[:, None]).reshape(-1).to(out.dtype)
+            memory[slot], normalizer[slot], maximum[slot] = S.to(memory.dtype), nz.to(normalizer.dtype), m.to(maximum.dtype)
