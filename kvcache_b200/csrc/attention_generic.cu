@@ -113,7 +113,8 @@ static int launch_generic(int dtype, const void* q, const void* k_pages, const v
                           int table_stride, const int* positions, const int* row_segment, void* out, int T, int Hq, int Hkv,
                           int D, int Dv, int page_size, int window, float scale, int* err, cudaStream_t stream) {
     if (T <= 0) return KVB_OK;
-    if (D > ATTN_MAX_D || D < 1 || Dv < 1 || Dv > D || Hkv < 1 || Hq % Hkv != 0) return KVB_ERR_SHAPE;
+    if (D > ATTN_MAX_D || D < 1 || Dv < 1 || Dv > ATTN_MAX_D || (Dv > D && v_pages == k_pages) || Hkv < 1 || Hq % Hkv != 0)
+        return KVB_ERR_SHAPE;
     const size_t smem = (size_t)(D + 2 * ATTN_THREADS + 33) * sizeof(float);
     dim3 grid(T, Hq);
     if (dtype == KVB_F32)
@@ -142,5 +143,14 @@ KVB_API int kvb_paged_attention_shared(int dtype, const void* q, const void* k_p
                                        const int* positions, const int* row_segment, void* out, int T, int Hq, int Hkv, int D,
                                        int Dv, int page_size, int window, float scale, int* err, cudaStream_t stream) {
     return launch_generic(dtype, q, k_pages, k_pages, block_table, table_stride, positions, row_segment, out, T, Hq, Hkv, D, Dv,
+                          page_size, window, scale, err, stream);
+}
+
+// Keys of D numbers and values of Dv numbers in pools of their own: out is [T, Hq * Dv].
+KVB_API int kvb_paged_attention_kv(int dtype, const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                                   int table_stride, const int* positions, const int* row_segment, void* out, int T, int Hq,
+                                   int Hkv, int D, int Dv, int page_size, int window, float scale, int* err, cudaStream_t stream) {
+    if (v_pages == k_pages) return KVB_ERR_SHAPE;
+    return launch_generic(dtype, q, k_pages, v_pages, block_table, table_stride, positions, row_segment, out, T, Hq, Hkv, D, Dv,
                           page_size, window, scale, err, stream);
 }

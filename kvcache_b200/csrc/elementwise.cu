@@ -281,8 +281,17 @@ KVB_API int kvb_add_rmsnorm(int dtype, float* h, const void* delta, const float*
 // out[r, i] = silu(gate[r, i]) * up[r, i],  silu(g) = g / (1 + exp(-g))   (src/qwen_kernels.cu:102-105).
 // gu[r, :] holds the gate and up projections of row r: [gate(I) | up(I)], or, interleaved in eights,
 // gate i at column 16 (i / 8) + i % 8 and up i eight columns further.
+// act 0: silu(g) * u.  act 1: g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit).
+__device__ __forceinline__ float gated_activation(float g, float u, int act, float limit) {
+    if (act == 0) return g / (1.f + expf(-g)) * u;
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+}
+
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total, int interleaved) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total, int interleaved, int act,
+                                float limit) {
     pdl_wait();
     pdl_launch_dependents();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -292,12 +301,13 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
         const int gcol = interleaved ? 16 * (i >> 3) + (i & 7) : i;
         const float g = to_f32<T>(gu[r * 2 * I + gcol]);
         const float u = to_f32<T>(gu[r * 2 * I + gcol + (interleaved ? 8 : I)]);
-        out[idx] = from_f32<T>(g / (1.f + expf(-g)) * u);
+        out[idx] = from_f32<T>(gated_activation(g, u, act, limit));
     }
 }
 
 // Eight outputs per thread and step: 16-byte loads of gate and up, one 16-byte (bfloat16) store.
-__global__ void silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I, size_t groups, int interleaved) {
+__global__ void silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I, size_t groups, int interleaved,
+                                     int act, float limit) {
     pdl_wait();
     pdl_launch_dependents();
     const int per_row = I >> 3;
@@ -313,15 +323,15 @@ __global__ void silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restri
         for (int k = 0; k < 4; ++k) {
             const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[k]));
             const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[k]));
-            __nv_bfloat162 o = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+            __nv_bfloat162 o = __floats2bfloat162_rn(gated_activation(g.x, u.x, act, limit), gated_activation(g.y, u.y, act, limit));
             ow[k] = *reinterpret_cast<uint32_t*>(&o);
         }
         *reinterpret_cast<uint4*>(out + r * I + 8 * b) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
 }
 
-KVB_API int kvb_silu_mul(int dtype, const void* gate_up, void* out, int T, int I, int interleaved, cudaStream_t stream) {
-    if (interleaved && I % 8 != 0) return KVB_ERR_SHAPE;
+static int gated_act(int dtype, const void* gate_up, void* out, int T, int I, int interleaved, int act, float limit, cudaStream_t stream) {
+    if ((interleaved && I % 8 != 0) || act < 0 || act > 1) return KVB_ERR_SHAPE;
     const size_t total = (size_t)T * I;
     if (total == 0) return KVB_OK;
     const int threads = 256;
@@ -332,14 +342,24 @@ KVB_API int kvb_silu_mul(int dtype, const void* gate_up, void* out, int T, int I
         const size_t groups = total / 8;
         size_t vblocks = (groups + threads - 1) / threads;
         if (vblocks > most) vblocks = most;
-        kvb_launch(silu_mul_vec8_kernel, dim3((int)vblocks), dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, I, groups, interleaved);
+        kvb_launch(silu_mul_vec8_kernel, dim3((int)vblocks), dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, I, groups, interleaved, act, limit);
         return kvb_launch_status();
     }
     if (dtype == KVB_F32)
-        kvb_launch(silu_mul_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, I, total, interleaved);
+        kvb_launch(silu_mul_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, I, total, interleaved, act, limit);
     else if (dtype == KVB_BF16)
-        kvb_launch(silu_mul_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, I, total, interleaved);
+        kvb_launch(silu_mul_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, I, total, interleaved, act, limit);
     else
         return KVB_ERR_DTYPE;
     return kvb_launch_status();
+}
+
+KVB_API int kvb_silu_mul(int dtype, const void* gate_up, void* out, int T, int I, int interleaved, cudaStream_t stream) {
+    return gated_act(dtype, gate_up, out, T, I, interleaved, 0, 0.f, stream);
+}
+
+// The gated activation by its code (see gated_activation) and constant.
+KVB_API int kvb_gated_act(int dtype, const void* gate_up, void* out, int T, int I, int interleaved, int act, float limit,
+                          cudaStream_t stream) {
+    return gated_act(dtype, gate_up, out, T, I, interleaved, act, limit, stream);
 }

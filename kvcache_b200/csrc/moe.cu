@@ -1,10 +1,11 @@
 // A routed feed-forward (mixture of experts) on the device, with launches that do not depend on the routing.
 //
-//   route_top      per row: the `top` experts with the largest float32 logits, weights = softmax over those logits only
+//   route_top      per row: the `top` experts with the largest float32 logits, weights = softmax over those logits only,
+//                  or the softmax over all experts' logits at the chosen ones, as they are
 //   routed_plan    (row, choice) pairs sorted by expert: where each pair sits, and the list of row tiles per expert
 //   grouped_gemm   for every tile: out[pair] = act(A[pair] . W[expert]^T); A gathered from the step's rows (the way up) or
 //                  read in sorted order (the way down); float32 accumulation on the CUDA cores
-//   routed_combine out[t] = sum_s weight[t, s] * y[place of pair (t, s)], float32, in the order of s
+//   routed_combine out[t] = base[t] + sum_s weight[t, s] * y[place of pair (t, s)], float32, in the order of s
 //
 // The grid of a grouped product is sized for the worst case, ceil(pairs / BM) + experts tiles; blocks beyond the
 // tiles that the plan made return at once.  A pair's result does not depend on where it sits in its tile, so the
@@ -15,8 +16,9 @@
 #define MOE_MAX_EXPERTS 1024
 
 // One warp per row.  Ties go to the lower expert index.
+// `over_all`: weights are exp(z - max) / sum over ALL experts (not renormalised over the chosen).
 __global__ void route_top_kernel(const float* __restrict__ logits, int* __restrict__ chosen, float* __restrict__ share, int T,
-                                 int E, int top) {
+                                 int E, int top, int over_all) {
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
@@ -30,6 +32,17 @@ __global__ void route_top_kernel(const float* __restrict__ logits, int* __restri
         z[c] = e < E ? logits[(size_t)r * E + e] : -FLT_MAX;
     }
     float first = 0.f, total = 0.f;
+    if (over_all) {
+        float biggest = -FLT_MAX;
+#pragma unroll
+        for (int c = 0; c < PER; ++c) biggest = fmaxf(biggest, z[c]);
+        biggest = warp_max(biggest);
+        float part = 0.f;
+#pragma unroll
+        for (int c = 0; c < PER; ++c)
+            if (lane + 32 * c < E) part += expf(z[c] - biggest);
+        total = warp_sum(part);
+    }
     for (int s = 0; s < top; ++s) {
         float best = -FLT_MAX;
         int arg = 0x7fffffff;
@@ -49,7 +62,7 @@ __global__ void route_top_kernel(const float* __restrict__ logits, int* __restri
             if (lane + 32 * c == arg) z[c] = -FLT_MAX;
         if (s == 0) first = best;                 // the largest of all: the softmax's reference point
         const float p = expf(best - first);
-        total += p;
+        if (!over_all) total += p;
         if (lane == 0) {
             chosen[(size_t)r * top + s] = arg;
             share[(size_t)r * top + s] = p;
@@ -60,12 +73,22 @@ __global__ void route_top_kernel(const float* __restrict__ logits, int* __restri
         for (int s = 0; s < top; ++s) share[(size_t)r * top + s] /= total;
 }
 
-KVB_API int kvb_route_top(const float* logits, int* chosen, float* share, int T, int E, int top, cudaStream_t stream) {
+static int launch_route_top(const float* logits, int* chosen, float* share, int T, int E, int top, int over_all, cudaStream_t stream) {
     if (T <= 0) return KVB_OK;
     if (E < 1 || E > MOE_MAX_EXPERTS || top < 1 || top > E) return KVB_ERR_SHAPE;
     const int warps = 4;
-    kvb_launch(route_top_kernel, dim3((T + warps - 1) / warps), dim3(32 * warps), 0, stream, logits, chosen, share, T, E, top);
+    kvb_launch(route_top_kernel, dim3((T + warps - 1) / warps), dim3(32 * warps), 0, stream, logits, chosen, share, T, E, top, over_all);
     return kvb_launch_status();
+}
+
+KVB_API int kvb_route_top(const float* logits, int* chosen, float* share, int T, int E, int top, cudaStream_t stream) {
+    return launch_route_top(logits, chosen, share, T, E, top, 0, stream);
+}
+
+// `over_all` 1: the weights are the softmax over all experts at the chosen ones.
+KVB_API int kvb_route_top_scores(const float* logits, int* chosen, float* share, int T, int E, int top, int over_all,
+                                 cudaStream_t stream) {
+    return launch_route_top(logits, chosen, share, T, E, top, over_all ? 1 : 0, stream);
 }
 
 // One block.  plan = [tile count | expert offsets (E + 1) | cursors (E)]; tiles[i] = (expert, first sorted row, rows).
@@ -121,12 +144,20 @@ KVB_API int kvb_routed_plan(const int* chosen, int pairs, int E, int BM, int pad
     return kvb_launch_status();
 }
 
-// ACT: 0 none, 1 relu(v)^2.  `gather_div` > 0: row i of A is x[sorted_pair[i] / gather_div]; 0: row i of A is a[i].
+// The clamped gated activation of a (gate, up) pair: g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit).
+__device__ __forceinline__ float clamped_swiglu(float g, float u, float limit) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+}
+
+// ACT: 0 none, 1 relu(v)^2, 2 the clamped gated activation of column pairs (2 i, 2 i + 1) = (gate i, up i): out has N / 2
+// columns.  `gather_div` > 0: row i of A is x[sorted_pair[i] / gather_div]; 0: row i of A is a[i].
 template <typename T, int BM, int ACT>
 __global__ void __launch_bounds__(256) grouped_gemm_simt_kernel(const T* __restrict__ a, const int* __restrict__ sorted_pair,
                                                                 int gather_div, const T* __restrict__ w, T* __restrict__ out,
                                                                 const int* __restrict__ plan, const int* __restrict__ tiles,
-                                                                int N, int K) {
+                                                                int N, int K, float limit) {
     pdl_wait();
     pdl_launch_dependents();
     if ((int)blockIdx.y >= plan[0]) return;
@@ -178,6 +209,14 @@ __global__ void __launch_bounds__(256) grouped_gemm_simt_kernel(const T* __restr
     for (int i = 0; i < TM; ++i) {
         const int row = ty * TM + i;
         if (row >= rows) continue;
+        if (ACT == 2) {
+#pragma unroll
+            for (int j = 0; j < 4; j += 2) {
+                const int gn = n0 + tx * 4 + j;
+                if (gn + 1 < N) out[(size_t)(row0 + row) * (N / 2) + gn / 2] = from_f32<T>(clamped_swiglu(acc[i][j], acc[i][j + 1], limit));
+            }
+            continue;
+        }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int gn = n0 + tx * 4 + j;
@@ -197,7 +236,7 @@ template <int MT, int ACT>
 __global__ void __launch_bounds__(mt::THREADS) grouped_gemm_mma_kernel(const bf16* __restrict__ a, const int* __restrict__ sorted_pair,
                                                                        int gather_div, const bf16* __restrict__ w,
                                                                        bf16* __restrict__ out, const int* __restrict__ plan,
-                                                                       const int* __restrict__ tiles, int N, int K) {
+                                                                       const int* __restrict__ tiles, int N, int K, float limit) {
     pdl_wait();
     pdl_launch_dependents();
     if ((int)blockIdx.y >= plan[0]) return;
@@ -213,6 +252,10 @@ __global__ void __launch_bounds__(mt::THREADS) grouped_gemm_mma_kernel(const bf1
     auto store = [&](int r, int c, float v0, float v1) {
         const int gn = n0 + c;
         if (r >= rows || gn >= N) return;
+        if (ACT == 2) {                 // columns gn (even) and gn + 1 are gate and up of index gn / 2
+            if (gn + 1 < N) out[(size_t)(row0 + r) * (N / 2) + gn / 2] = __float2bfloat16_rn(clamped_swiglu(v0, v1, limit));
+            return;
+        }
         if (ACT == 1) {
             v0 = fmaxf(v0, 0.f); v0 *= v0;
             v1 = fmaxf(v1, 0.f); v1 *= v1;
@@ -226,23 +269,24 @@ __global__ void __launch_bounds__(mt::THREADS) grouped_gemm_mma_kernel(const bf1
 
 template <typename T, int BM>
 static void launch_grouped(const T* a, const int* sorted_pair, int gather_div, const T* w, T* out, const int* plan,
-                           const int* tiles, int max_tiles, int N, int K, int act, cudaStream_t stream) {
+                           const int* tiles, int max_tiles, int N, int K, int act, float limit, cudaStream_t stream) {
     dim3 grid((N + 63) / 64, max_tiles);
-    if (act == 1)
-        kvb_launch(grouped_gemm_simt_kernel<T, BM, 1>, grid, dim3(256), 0, stream, a, sorted_pair, gather_div, w, out, plan, tiles, N, K);
+    if (act == 2)
+        kvb_launch(grouped_gemm_simt_kernel<T, BM, 2>, grid, dim3(256), 0, stream, a, sorted_pair, gather_div, w, out, plan, tiles, N, K, limit);
+    else if (act == 1)
+        kvb_launch(grouped_gemm_simt_kernel<T, BM, 1>, grid, dim3(256), 0, stream, a, sorted_pair, gather_div, w, out, plan, tiles, N, K, limit);
     else
-        kvb_launch(grouped_gemm_simt_kernel<T, BM, 0>, grid, dim3(256), 0, stream, a, sorted_pair, gather_div, w, out, plan, tiles, N, K);
+        kvb_launch(grouped_gemm_simt_kernel<T, BM, 0>, grid, dim3(256), 0, stream, a, sorted_pair, gather_div, w, out, plan, tiles, N, K, limit);
 }
 
-// `BM` must be the one the plan was made with (16 or 64).
-KVB_API int kvb_grouped_gemm(int dtype, const void* a, const int* sorted_pair, int gather_div, const void* w, void* out,
-                             const int* plan, const int* tiles, int max_tiles, int BM, int N, int K, int act,
-                             cudaStream_t stream) {
+static int grouped_gemm(int dtype, const void* a, const int* sorted_pair, int gather_div, const void* w, void* out,
+                        const int* plan, const int* tiles, int max_tiles, int BM, int N, int K, int act, float limit,
+                        cudaStream_t stream) {
     if (max_tiles <= 0) return KVB_OK;
-    if (N < 1 || K < 1 || (BM != 16 && BM != 64) || act < 0 || act > 1) return KVB_ERR_SHAPE;
+    if (N < 1 || K < 1 || (BM != 16 && BM != 64) || act < 0 || act > 2 || (act == 2 && N % 2 != 0)) return KVB_ERR_SHAPE;
     if (max_tiles > 65535) return KVB_ERR_LIMIT;
 #define KVB_GROUPED(T, BM_)                                                                                                  \
-    launch_grouped<T, BM_>((const T*)a, sorted_pair, gather_div, (const T*)w, (T*)out, plan, tiles, max_tiles, N, K, act, stream)
+    launch_grouped<T, BM_>((const T*)a, sorted_pair, gather_div, (const T*)w, (T*)out, plan, tiles, max_tiles, N, K, act, limit, stream)
     if (dtype == KVB_F32) {
         if (BM == 16) KVB_GROUPED(float, 16); else KVB_GROUPED(float, 64);
     } else if (dtype == KVB_BF16) {
@@ -251,9 +295,9 @@ KVB_API int kvb_grouped_gemm(int dtype, const void* a, const int* sorted_pair, i
             dim3 grid((N + 63) / 64, max_tiles);
             const bf16 *ab = (const bf16*)a, *wb = (const bf16*)w;
 #define KVB_GROUPED_MMA(MT, ACT_) \
-    kvb_launch(grouped_gemm_mma_kernel<MT, ACT_>, grid, dim3(mt::THREADS), 0, stream, ab, sorted_pair, gather_div, wb, (bf16*)out, plan, tiles, N, K)
-            if (BM == 16) { if (act == 1) KVB_GROUPED_MMA(1, 1); else KVB_GROUPED_MMA(1, 0); }
-            else { if (act == 1) KVB_GROUPED_MMA(4, 1); else KVB_GROUPED_MMA(4, 0); }
+    kvb_launch(grouped_gemm_mma_kernel<MT, ACT_>, grid, dim3(mt::THREADS), 0, stream, ab, sorted_pair, gather_div, wb, (bf16*)out, plan, tiles, N, K, limit)
+            if (BM == 16) { if (act == 2) KVB_GROUPED_MMA(1, 2); else if (act == 1) KVB_GROUPED_MMA(1, 1); else KVB_GROUPED_MMA(1, 0); }
+            else { if (act == 2) KVB_GROUPED_MMA(4, 2); else if (act == 1) KVB_GROUPED_MMA(4, 1); else KVB_GROUPED_MMA(4, 0); }
 #undef KVB_GROUPED_MMA
         } else if (BM == 16) {
             KVB_GROUPED(bf16, 16);
@@ -267,28 +311,56 @@ KVB_API int kvb_grouped_gemm(int dtype, const void* a, const int* sorted_pair, i
     return kvb_launch_status();
 }
 
-// out[t, :] = sum_s share[t, s] * y[place[t * top + s], :]
+// `BM` must be the one the plan was made with (16 or 64).
+KVB_API int kvb_grouped_gemm(int dtype, const void* a, const int* sorted_pair, int gather_div, const void* w, void* out,
+                             const int* plan, const int* tiles, int max_tiles, int BM, int N, int K, int act,
+                             cudaStream_t stream) {
+    if (act > 1) return KVB_ERR_SHAPE;
+    return grouped_gemm(dtype, a, sorted_pair, gather_div, w, out, plan, tiles, max_tiles, BM, N, K, act, 0.f, stream);
+}
+
+// The same with the activation's constant: act 2 is the clamped gated activation with `limit`, out [rows, N / 2].
+KVB_API int kvb_grouped_gemm_act(int dtype, const void* a, const int* sorted_pair, int gather_div, const void* w, void* out,
+                                 const int* plan, const int* tiles, int max_tiles, int BM, int N, int K, int act, float limit,
+                                 cudaStream_t stream) {
+    return grouped_gemm(dtype, a, sorted_pair, gather_div, w, out, plan, tiles, max_tiles, BM, N, K, act, limit, stream);
+}
+
+// out[t, :] = base[t, :] (if given) + sum_s share[t, s] * y[place[t * top + s], :]
 template <typename T>
 __global__ void routed_combine_kernel(const T* __restrict__ y, const int* __restrict__ place, const float* __restrict__ share,
-                                      T* __restrict__ out, int top, int H) {
+                                      const T* __restrict__ base, T* __restrict__ out, int top, int H) {
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = 0.f;
+        float v = base ? to_f32<T>(base[(size_t)t * H + i]) : 0.f;
         for (int s = 0; s < top; ++s) v += share[(size_t)t * top + s] * to_f32<T>(y[(size_t)place[(size_t)t * top + s] * H + i]);
         out[(size_t)t * H + i] = from_f32<T>(v);
     }
 }
 
-KVB_API int kvb_routed_combine(int dtype, const void* y, const int* place, const float* share, void* out, int T, int top, int H,
-                               cudaStream_t stream) {
+static int routed_combine(int dtype, const void* y, const int* place, const float* share, const void* base, void* out, int T, int top,
+                          int H, cudaStream_t stream) {
     if (T <= 0) return KVB_OK;
     if (dtype == KVB_F32)
-        kvb_launch(routed_combine_kernel<float>, dim3(T), dim3(128), 0, stream, (const float*)y, place, share, (float*)out, top, H);
+        kvb_launch(routed_combine_kernel<float>, dim3(T), dim3(128), 0, stream, (const float*)y, place, share, (const float*)base,
+                   (float*)out, top, H);
     else if (dtype == KVB_BF16)
-        kvb_launch(routed_combine_kernel<bf16>, dim3(T), dim3(128), 0, stream, (const bf16*)y, place, share, (bf16*)out, top, H);
+        kvb_launch(routed_combine_kernel<bf16>, dim3(T), dim3(128), 0, stream, (const bf16*)y, place, share, (const bf16*)base,
+                   (bf16*)out, top, H);
     else
         return KVB_ERR_DTYPE;
     return kvb_launch_status();
+}
+
+KVB_API int kvb_routed_combine(int dtype, const void* y, const int* place, const float* share, void* out, int T, int top, int H,
+                               cudaStream_t stream) {
+    return routed_combine(dtype, y, place, share, nullptr, out, T, top, H, stream);
+}
+
+// The same on top of `base` [T, H] (what every row takes besides its experts).
+KVB_API int kvb_routed_combine_base(int dtype, const void* y, const int* place, const float* share, const void* base, void* out,
+                                    int T, int top, int H, cudaStream_t stream) {
+    return routed_combine(dtype, y, place, share, base, out, T, top, H, stream);
 }

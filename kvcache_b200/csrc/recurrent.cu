@@ -1,0 +1,320 @@
+// Operators of mixers that carry a matrix per request and head from token to token, of gated heads, and of the
+// hashed pair embedding.
+//
+//   matrix_state_scan   S_t = decay_t S_{t-1} + gain_t k_t v_t^T, o_t = S_t^T q_t over the tokens of every segment, from
+//                       and into the request's state slot; two forms of decay (below)
+//   head_norm_gate      out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w * act(gate[t, h, :]) * scale
+//   head_gate           out[t, h, :] = x[t, h, :] * sigmoid(gate[t, h]) * scale
+//   bigram_embed        h[r] += table[(previous token * a + token * b) mod buckets], the table's last row at position 0;
+//                       then the request's previous token becomes the last one of its segment
+//
+// The scan keeps everything in float32.  A warp owns CPW value channels (columns of S) of one head; lane l holds the
+// key channels l, l + 32, ... of those columns in registers for the whole segment, so a token costs two fused
+// multiply-adds per held number, one shuffle tree per column, and no barrier.  A column's sum over the key channels
+// is taken in one order (lane-local over l + 32 i, then the xor tree), whatever the step holds: a token's result is
+// bit for bit the same in a prompt, a portion or alone.  State layout: [slot, head, value channel, key channel].
+#include "common.cuh"
+
+enum { SCAN_CHANNEL_DECAY = 0, SCAN_EXP_GATES = 1 };
+
+__device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+// SCAN_CHANNEL_DECAY: decay per key channel d = sigmoid(z[r, h, d])^(1 / p0)  (z: `gate`, row stride gate_stride), gain 1.
+// SCAN_EXP_GATES:     per head i = p0 tanh(gate[r, g0 + h] / p0), f = logsigmoid(p0 tanh(gate[r, g1 + h] / p0));
+//                     m' = max(f + m, i); decay e^{f + m - m'}, gain e^{i - m'}; n' = decay n + gain k;
+//                     o = S'^T q / (max(|n' . q|, e^{-m'}) + floor).  n: [slot, head, key channel], m: [slot, head].
+// grid (column blocks, heads, segments); the exponential-gate form takes one block per head (its n and m are read by
+// every warp at the start and written by the first at the end, with a barrier in between).
+template <int MODE, int RPL, int CPW>
+__global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 1024 : 256) matrix_state_scan_kernel(
+    const float* __restrict__ proj, int P, int q_col, int k_col, int v_col, const float* __restrict__ gate, int gate_stride,
+    int g0, int g1, float p0, float q_scale, float floor_, const int* __restrict__ seg_q_start,
+    const int* __restrict__ seg_q_len, const int* __restrict__ seg_slot, float* __restrict__ memory,
+    float* __restrict__ normalizer, float* __restrict__ maximum, float* __restrict__ out, int H, int D, int Dv) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int h = blockIdx.y, seg = blockIdx.z;
+    const int c0 = (blockIdx.x * warps + warp) * CPW;
+    const int r0 = seg_q_start[seg], n_rows = seg_q_len[seg], slot = seg_slot[seg];
+    pdl_wait();
+    pdl_launch_dependents();
+    float S[CPW][RPL], nz[RPL], m = 0.f;
+    float* mem = memory + ((size_t)slot * H + h) * Dv * D;
+#pragma unroll
+    for (int c = 0; c < CPW; ++c)
+#pragma unroll
+        for (int i = 0; i < RPL; ++i) {
+            const int d = lane + 32 * i;
+            S[c][i] = (c0 + c < Dv && d < D) ? mem[(size_t)(c0 + c) * D + d] : 0.f;
+        }
+    if (MODE == SCAN_EXP_GATES) {
+#pragma unroll
+        for (int i = 0; i < RPL; ++i) {
+            const int d = lane + 32 * i;
+            nz[i] = d < D ? normalizer[((size_t)slot * H + h) * D + d] : 0.f;
+        }
+        m = maximum[(size_t)slot * H + h];
+        __syncthreads();                      // every warp has read n and m before the first may write them
+    }
+    // The rows of the next token are fetched while this one is computed: none of them depends on the state.
+    float q[RPL], k[RPL], a[RPL], v[CPW], gi = 0.f, gf = 0.f;
+    auto fetch = [&](int r) {
+        const float* row = proj + (size_t)r * P;
+#pragma unroll
+        for (int i = 0; i < RPL; ++i) {
+            const int d = lane + 32 * i;
+            q[i] = d < D ? row[q_col + h * D + d] : 0.f;
+            k[i] = d < D ? row[k_col + h * D + d] : 0.f;
+            if (MODE == SCAN_CHANNEL_DECAY) a[i] = d < D ? gate[(size_t)r * gate_stride + g0 + h * D + d] : 0.f;
+        }
+#pragma unroll
+        for (int c = 0; c < CPW; ++c) v[c] = c0 + c < Dv ? row[v_col + h * Dv + c0 + c] : 0.f;
+        if (MODE == SCAN_EXP_GATES) {
+            gi = gate[(size_t)r * gate_stride + g0 + h];
+            gf = gate[(size_t)r * gate_stride + g1 + h];
+        }
+    };
+    if (n_rows > 0) fetch(r0);
+    for (int t = 0; t < n_rows; ++t) {
+        const int r = r0 + t;
+        float qc[RPL], kc[RPL], ac[RPL], vc[CPW];
+        const float gic = gi, gfc = gf;
+#pragma unroll
+        for (int i = 0; i < RPL; ++i) { qc[i] = q[i] * q_scale; kc[i] = k[i]; ac[i] = a[i]; }
+#pragma unroll
+        for (int c = 0; c < CPW; ++c) vc[c] = v[c];
+        if (t + 1 < n_rows) fetch(r + 1);
+        float keep = 1.f, take = 1.f, denom = 1.f;
+        if (MODE == SCAN_CHANNEL_DECAY) {
+#pragma unroll
+            for (int i = 0; i < RPL; ++i) ac[i] = expf(log_sigmoid(ac[i]) / p0);
+        } else {
+            const float li = p0 * tanhf(gic / p0), lf = log_sigmoid(p0 * tanhf(gfc / p0));
+            const float m_new = fmaxf(lf + m, li);
+            keep = expf(lf + m - m_new);
+            take = expf(li - m_new);
+            m = m_new;
+            float part = 0.f;
+#pragma unroll
+            for (int i = 0; i < RPL; ++i) {
+                nz[i] = keep * nz[i] + take * kc[i];
+                part += nz[i] * qc[i];
+            }
+            denom = fmaxf(fabsf(warp_sum(part)), expf(-m_new)) + floor_;
+        }
+        float o[CPW];
+#pragma unroll
+        for (int c = 0; c < CPW; ++c) {
+            float part = 0.f;
+#pragma unroll
+            for (int i = 0; i < RPL; ++i) {
+                if (MODE == SCAN_CHANNEL_DECAY) S[c][i] = ac[i] * S[c][i] + kc[i] * vc[c];
+                else S[c][i] = keep * S[c][i] + take * (kc[i] * vc[c]);
+                part += S[c][i] * qc[i];
+            }
+            o[c] = warp_sum(part);
+            if (MODE == SCAN_EXP_GATES) o[c] = o[c] / denom;
+        }
+#pragma unroll
+        for (int c = 0; c < CPW; ++c)
+            if (lane == c && c0 + c < Dv) out[(size_t)r * H * Dv + h * Dv + c0 + c] = o[c];
+    }
+    if (n_rows <= 0) return;
+#pragma unroll
+    for (int c = 0; c < CPW; ++c)
+#pragma unroll
+        for (int i = 0; i < RPL; ++i) {
+            const int d = lane + 32 * i;
+            if (c0 + c < Dv && d < D) mem[(size_t)(c0 + c) * D + d] = S[c][i];
+        }
+    if (MODE == SCAN_EXP_GATES && blockIdx.x == 0 && warp == 0) {
+#pragma unroll
+        for (int i = 0; i < RPL; ++i) {
+            const int d = lane + 32 * i;
+            if (d < D) normalizer[((size_t)slot * H + h) * D + d] = nz[i];
+        }
+        if (lane == 0) maximum[(size_t)slot * H + h] = m;
+    }
+}
+
+template <int MODE, int RPL, int CPW>
+static void launch_scan(const float* proj, int P, int q_col, int k_col, int v_col, const float* gate, int gate_stride, int g0, int g1,
+                        float p0, float q_scale, float floor_, const int* seg_q_start, const int* seg_q_len, const int* seg_slot,
+                        float* memory, float* normalizer, float* maximum, float* out, int S, int H, int D, int Dv, cudaStream_t stream) {
+    const int total_warps = (Dv + CPW - 1) / CPW;
+    // The exponential-gate form: all of a head's columns in one block.  The other: blocks of up to 8 warps.
+    const int warps = MODE == SCAN_EXP_GATES ? total_warps : (total_warps < 8 ? total_warps : 8);
+    dim3 grid((total_warps + warps - 1) / warps, H, S);
+    kvb_launch(matrix_state_scan_kernel<MODE, RPL, CPW>, grid, dim3(32 * warps), 0, stream, proj, P, q_col, k_col, v_col, gate,
+               gate_stride, g0, g1, p0, q_scale, floor_, seg_q_start, seg_q_len, seg_slot, memory, normalizer, maximum, out, H, D, Dv);
+}
+
+// proj: float32 [T, P] with q at q_col (H * D numbers), k at k_col, v at v_col (H * Dv).  `gate`: float32 rows of
+// stride gate_stride - per-channel decay logits at g0 (mode 0), or the two gates' pre-activations at g0 and g1 (mode 1).
+KVB_API int kvb_matrix_state_scan(int mode, const float* proj, int P, int q_col, int k_col, int v_col, const float* gate,
+                                  int gate_stride, int g0, int g1, float p0, float q_scale, float floor_, const int* seg_q_start,
+                                  const int* seg_q_len, const int* seg_slot, float* memory, float* normalizer, float* maximum,
+                                  float* out, int S, int H, int D, int Dv, cudaStream_t stream) {
+    if (S <= 0) return KVB_OK;
+    if (H < 1 || D < 1 || Dv < 1 || (mode != SCAN_CHANNEL_DECAY && mode != SCAN_EXP_GATES)) return KVB_ERR_SHAPE;
+    if (D > 256 || Dv > 256 || H > 65535 || S > 65535) return KVB_ERR_LIMIT;
+    const int rpl = D <= 32 ? 1 : D <= 64 ? 2 : D <= 128 ? 4 : 8;
+    const int cpw = Dv <= 32 ? 1 : Dv <= 128 ? 4 : 8;
+#define KVB_SCAN(MODE, RPL, CPW)                                                                                              \
+    launch_scan<MODE, RPL, CPW>(proj, P, q_col, k_col, v_col, gate, gate_stride, g0, g1, p0, q_scale, floor_, seg_q_start,     \
+                                seg_q_len, seg_slot, memory, normalizer, maximum, out, S, H, D, Dv, stream)
+#define KVB_SCAN_CPW(MODE, RPL)                                                                                               \
+    do {                                                                                                                      \
+        if (cpw == 1) KVB_SCAN(MODE, RPL, 1); else if (cpw == 4) KVB_SCAN(MODE, RPL, 4); else KVB_SCAN(MODE, RPL, 8);         \
+    } while (0)
+#define KVB_SCAN_RPL(MODE)                                                                                                    \
+    do {                                                                                                                      \
+        if (rpl == 1) KVB_SCAN_CPW(MODE, 1); else if (rpl == 2) KVB_SCAN_CPW(MODE, 2);                                        \
+        else if (rpl == 4) KVB_SCAN_CPW(MODE, 4); else KVB_SCAN_CPW(MODE, 8);                                                 \
+    } while (0)
+    if (mode == SCAN_CHANNEL_DECAY) KVB_SCAN_RPL(SCAN_CHANNEL_DECAY); else KVB_SCAN_RPL(SCAN_EXP_GATES);
+#undef KVB_SCAN_RPL
+#undef KVB_SCAN_CPW
+#undef KVB_SCAN
+    return kvb_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// One warp per (row, head).  o: float32 [T, H * Dv]; w: [Dv] (shared by the heads) or [H * Dv] (w_per_head);
+// gate: float32 rows of stride gate_stride, the head's Dv numbers at gate_col + h * Dv; act 0: silu, 1: sigmoid.
+// out (type T) rows of stride out_stride, written at out_col + h * Dv.
+template <typename T>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, int w_per_head, float eps,
+                                      const float* __restrict__ gate, int gate_stride, int gate_col, int act, float scale,
+                                      T* __restrict__ out, int out_stride, int out_col, int pairs, int H, int Dv) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (pair >= pairs) return;
+    const int t = pair / H, h = pair - t * H;
+    const float* src = o + (size_t)t * H * Dv + (size_t)h * Dv;
+    float ss = 0.f;
+    for (int d = lane; d < Dv; d += 32) ss += src[d] * src[d];
+    const float inv = 1.f / sqrtf(warp_sum(ss) / (float)Dv + eps);
+    const float* g = gate + (size_t)t * gate_stride + gate_col + h * Dv;
+    const float* wh = w + (w_per_head ? h * Dv : 0);
+    T* dst = out + (size_t)t * out_stride + out_col + h * Dv;
+    for (int d = lane; d < Dv; d += 32) {
+        const float z = g[d];
+        const float s = 1.f / (1.f + expf(-z));
+        dst[d] = from_f32<T>(src[d] * inv * wh[d] * (act == 0 ? z * s : s) * scale);
+    }
+}
+
+KVB_API int kvb_head_norm_gate(int out_dtype, const float* o, const float* w, int w_per_head, float eps, const float* gate,
+                               int gate_stride, int gate_col, int act, float scale, void* out, int out_stride, int out_col,
+                               int T, int H, int Dv, cudaStream_t stream) {
+    if (T <= 0) return KVB_OK;
+    if (H < 1 || Dv < 1 || act < 0 || act > 1) return KVB_ERR_SHAPE;
+    const int pairs = T * H, warps = 4;
+    dim3 grid((pairs + warps - 1) / warps), block(32 * warps);
+    if (out_dtype == KVB_F32)
+        kvb_launch(head_norm_gate_kernel<float>, grid, block, 0, stream, o, w, w_per_head, eps, gate, gate_stride, gate_col, act, scale,
+                   (float*)out, out_stride, out_col, pairs, H, Dv);
+    else if (out_dtype == KVB_BF16)
+        kvb_launch(head_norm_gate_kernel<bf16>, grid, block, 0, stream, o, w, w_per_head, eps, gate, gate_stride, gate_col, act, scale,
+                   (bf16*)out, out_stride, out_col, pairs, H, Dv);
+    else
+        return KVB_ERR_DTYPE;
+    return kvb_launch_status();
+}
+
+// out[t, out_col + h * Dv + d] = x[t, h * Dv + d] * sigmoid(gate[t, gate_col + h]) * scale (gate null: no sigmoid).
+template <typename T>
+__global__ void head_gate_kernel(const T* __restrict__ x, const T* __restrict__ gate, int gate_stride, int gate_col, float scale,
+                                 T* __restrict__ out, int out_stride, int out_col, int H, int Dv, size_t total) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int width = H * Dv;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / width;
+        const int c = (int)(idx - t * width);
+        float v = to_f32<T>(x[idx]) * scale;
+        if (gate) v *= 1.f / (1.f + expf(-to_f32<T>(gate[t * gate_stride + gate_col + c / Dv])));
+        out[t * out_stride + out_col + c] = from_f32<T>(v);
+    }
+}
+
+KVB_API int kvb_head_gate(int dtype, const void* x, const void* gate, int gate_stride, int gate_col, float scale, void* out,
+                          int out_stride, int out_col, int T, int H, int Dv, cudaStream_t stream) {
+    const size_t total = (size_t)T * H * Dv;
+    if (total == 0) return KVB_OK;
+    size_t blocks = (total + 255) / 256;
+    const size_t most = (size_t)kvb_sm_count() * 16;
+    if (blocks > most) blocks = most;
+    if (dtype == KVB_F32)
+        kvb_launch(head_gate_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (const float*)x, (const float*)gate, gate_stride,
+                   gate_col, scale, (float*)out, out_stride, out_col, H, Dv, total);
+    else if (dtype == KVB_BF16)
+        kvb_launch(head_gate_kernel<bf16>, dim3((int)blocks), dim3(256), 0, stream, (const bf16*)x, (const bf16*)gate, gate_stride,
+                   gate_col, scale, (bf16*)out, out_stride, out_col, H, Dv, total);
+    else
+        return KVB_ERR_DTYPE;
+    return kvb_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ int token_of(const int* ids, const int* src, const int* last, int r) {
+    const int from = src ? src[r] : -1;
+    return from >= 0 ? last[from] : ids[r];
+}
+
+// One block per row.  A token outside the vocabulary adds nothing (the embedding kernel has flagged it).
+template <typename T>
+__global__ void bigram_embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, const int* __restrict__ src,
+                                    const int* __restrict__ last, const int* __restrict__ positions,
+                                    const int* __restrict__ row_segment, const int* __restrict__ seg_q_start,
+                                    const int* __restrict__ seg_slot, const int* __restrict__ previous, float* __restrict__ h,
+                                    int W, int buckets, int mul_prev, int mul_cur, int V) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    const int tok = token_of(ids, src, last, r);
+    if (tok < 0 || tok >= V) return;
+    int row = buckets;
+    if (positions[r] > 0) {
+        const int seg = row_segment[r];
+        const int before = r > seg_q_start[seg] ? token_of(ids, src, last, r - 1) : previous[seg_slot[seg]];
+        row = (int)(((long long)before * mul_prev + (long long)tok * mul_cur) % buckets);
+        if (row < 0) row += buckets;
+    }
+    const T* add = table + (size_t)row * W;
+    float* dst = h + (size_t)r * W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) dst[i] += to_f32<T>(add[i]);
+}
+
+__global__ void previous_token_kernel(const int* __restrict__ ids, const int* __restrict__ src, const int* __restrict__ last,
+                                      const int* __restrict__ seg_q_start, const int* __restrict__ seg_q_len,
+                                      const int* __restrict__ seg_slot, int* __restrict__ previous, int S) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s < S && seg_q_len[s] > 0) previous[seg_slot[s]] = token_of(ids, src, last, seg_q_start[s] + seg_q_len[s] - 1);
+}
+
+KVB_API int kvb_bigram_embed(int dtype, const void* table, const int* ids, const int* src, const int* last, const int* positions,
+                             const int* row_segment, const int* seg_q_start, const int* seg_q_len, const int* seg_slot,
+                             int* previous, float* h, int T, int S, int W, int buckets, int mul_prev, int mul_cur, int V,
+                             cudaStream_t stream) {
+    if (T <= 0) return KVB_OK;
+    if (buckets < 1 || W < 1) return KVB_ERR_SHAPE;
+    const int threads = W >= 512 ? 256 : 128;
+    if (dtype == KVB_F32)
+        kvb_launch(bigram_embed_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, ids, src, last, positions,
+                   row_segment, seg_q_start, seg_slot, previous, h, W, buckets, mul_prev, mul_cur, V);
+    else if (dtype == KVB_BF16)
+        kvb_launch(bigram_embed_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16*)table, ids, src, last, positions,
+                   row_segment, seg_q_start, seg_slot, previous, h, W, buckets, mul_prev, mul_cur, V);
+    else
+        return KVB_ERR_DTYPE;
+    int status = kvb_launch_status();
+    if (status != KVB_OK) return status;
+    kvb_launch(previous_token_kernel, dim3((S + 127) / 128), dim3(128), 0, stream, ids, src, last, seg_q_start, seg_q_len, seg_slot,
+               previous, S);
+    return kvb_launch_status();
+}

@@ -317,3 +317,102 @@ KVB_API int kvb_qkv_rope_append(int dtype, const void* qkv, const float* bias, c
         return KVB_ERR_DTYPE;
     return kvb_launch_status();
 }
+
+// The same for layers whose queries and keys are normalised per head before the rotation, whose values have another
+// size than their keys, or whose projection carries further columns: rows of `qkv` are
+// [Hq heads of D | Hkv heads of D | Hkv heads of Dv | ...] with stride `row_stride`.  A query or key head becomes
+// x / sqrt(mean(x^2) + eps) * w (w: D numbers shared by the heads; null: as it is), then its first 2 * rot_half numbers
+// are rotated.  One block per row, a warp per head in turn; the normalised head passes through shared memory so that a
+// lane finds its rotation partner.  Value pages are [pages, Hkv, page_size, Dv].
+template <typename T>
+__global__ void qkv_norm_rope_append_kernel(const T* __restrict__ qkv, int row_stride, const float* __restrict__ bias,
+                                            const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                            const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_half,
+                                            int table_len, const int* __restrict__ positions, const int* __restrict__ row_segment,
+                                            const int* __restrict__ block_table, int table_stride, T* __restrict__ k_pages,
+                                            T* __restrict__ v_pages, T* __restrict__ q_out, int Hq, int Hkv, int D, int Dv,
+                                            int page_size, int write_kv, int* __restrict__ err) {
+    extern __shared__ float head_s[];          // [warps][D]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int r = blockIdx.x;
+    const int pos = positions[r];
+    long long page_row = -1;                   // (page, slot) of the row's keys and values, counted in tokens
+    if (write_kv) {
+        const int page = block_table[(size_t)row_segment[r] * table_stride + pos / page_size];
+        if (page < 0) {
+            if (threadIdx.x == 0) atomicOr(err, KVB_DEV_BAD_PAGE);
+        } else {
+            page_row = (long long)page * Hkv * page_size + (pos % page_size);
+        }
+    }
+    const bool pos_ok = rot_half == 0 || (pos >= 0 && pos < table_len);
+    if (!pos_ok && threadIdx.x == 0) atomicOr(err, KVB_DEV_BAD_POS);
+    const float* cr = cos_t + (size_t)(pos_ok ? pos : 0) * rot_half;
+    const float* sr = sin_t + (size_t)(pos_ok ? pos : 0) * rot_half;
+    pdl_wait();
+    pdl_launch_dependents();
+    const T* src = qkv + (size_t)r * row_stride;
+    float* mine = head_s + (size_t)warp * D;
+    for (int head = warp; head < Hq + Hkv; head += warps) {
+        const T* x = src + (size_t)head * D;
+        const float* b = bias ? bias + (size_t)head * D : nullptr;
+        const float* w = head < Hq ? q_w : k_w;
+        float ss = 0.f;
+        for (int d = lane; d < D; d += 32) {
+            const float v = to_f32<T>(x[d]) + (b ? b[d] : 0.f);
+            mine[d] = v;
+            ss += v * v;
+        }
+        const float inv = w ? 1.f / sqrtf(warp_sum(ss) / (float)D + eps) : 1.f;
+        if (w)
+            for (int d = lane; d < D; d += 32) mine[d] = mine[d] * inv * w[d];
+        __syncwarp();
+        T* dst = nullptr;
+        if (head < Hq) dst = q_out + ((size_t)r * Hq + head) * D;
+        else if (page_row >= 0) dst = k_pages + ((size_t)page_row + (size_t)(head - Hq) * page_size) * D;
+        if (dst)
+            for (int d = lane; d < D; d += 32) {
+                float v = mine[d];
+                if (d < 2 * rot_half) {
+                    const bool low = d < rot_half;
+                    const int t = low ? d : d - rot_half;
+                    const float p = mine[low ? d + rot_half : d - rot_half];
+                    v = low ? v * cr[t] - p * sr[t] : v * cr[t] + p * sr[t];
+                }
+                dst[d] = from_f32<T>(v);
+            }
+        __syncwarp();
+    }
+    if (page_row >= 0) {
+        const T* v_src = src + (size_t)(Hq + Hkv) * D;
+        const float* b = bias ? bias + (size_t)(Hq + Hkv) * D : nullptr;
+        for (int i = threadIdx.x; i < Hkv * Dv; i += blockDim.x) {
+            const int hk = i / Dv, d = i - hk * Dv;
+            v_pages[((size_t)page_row + (size_t)hk * page_size) * Dv + d] = from_f32<T>(to_f32<T>(v_src[i]) + (b ? b[i] : 0.f));
+        }
+    }
+}
+
+KVB_API int kvb_qkv_norm_rope_append(int dtype, const void* qkv, int row_stride, const float* bias, const float* q_w,
+                                     const float* k_w, float eps, const float* cos_t, const float* sin_t, int rot_half,
+                                     int table_len, const int* positions, const int* row_segment, const int* block_table,
+                                     int table_stride, void* k_pages, void* v_pages, void* q_out, int T, int Hq, int Hkv, int D,
+                                     int Dv, int page_size, int write_kv, int* err, cudaStream_t stream) {
+    if (T <= 0) return KVB_OK;
+    if (2 * rot_half > D || rot_half < 0 || Dv < 1 || row_stride < (Hq + Hkv) * D + Hkv * Dv || (q_w == nullptr) != (k_w == nullptr))
+        return KVB_ERR_SHAPE;
+    const int warps = Hq + Hkv >= 8 ? 8 : 4;
+    const size_t smem = (size_t)warps * D * sizeof(float);
+    if (smem > 48 * 1024) return KVB_ERR_LIMIT;
+    if (dtype == KVB_F32)
+        kvb_launch(qkv_norm_rope_append_kernel<float>, dim3(T), dim3(32 * warps), smem, stream, (const float*)qkv, row_stride, bias,
+                   q_w, k_w, eps, cos_t, sin_t, rot_half, table_len, positions, row_segment, block_table, table_stride,
+                   (float*)k_pages, (float*)v_pages, (float*)q_out, Hq, Hkv, D, Dv, page_size, write_kv, err);
+    else if (dtype == KVB_BF16)
+        kvb_launch(qkv_norm_rope_append_kernel<bf16>, dim3(T), dim3(32 * warps), smem, stream, (const bf16*)qkv, row_stride, bias,
+                   q_w, k_w, eps, cos_t, sin_t, rot_half, table_len, positions, row_segment, block_table, table_stride,
+                   (bf16*)k_pages, (bf16*)v_pages, (bf16*)q_out, Hq, Hkv, D, Dv, page_size, write_kv, err);
+    else
+        return KVB_ERR_DTYPE;
+    return kvb_launch_status();
+}

@@ -90,13 +90,30 @@ _SIGNATURES = {
         "kvb_embed": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
         "kvb_add_rmsnorm": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p],
         "kvb_silu_mul": [_c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+        "kvb_gated_act": [_c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
     },
     "rope_append": {
         "kvb_qkv_rope_append": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p,
                                 _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
                                 _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+        "kvb_qkv_norm_rope_append": [_c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_int,
+                                     _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
+                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    },
+    "recurrent": {
+        "kvb_matrix_state_scan": [_c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_float,
+                                  _c_float, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                                  _c_int, _c_int, _c_int, _c_int, _c_void_p],
+        "kvb_head_norm_gate": [_c_int, _c_void_p, _c_void_p, _c_int, _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p,
+                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+        "kvb_head_gate": [_c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                          _c_void_p],
+        "kvb_bigram_embed": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                             _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     },
     "attention_generic": {
+        "kvb_paged_attention_kv": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
         "kvb_paged_attention_generic": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
                                         _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                         _c_float, _c_void_p, _c_void_p],
@@ -125,6 +142,10 @@ _SIGNATURES = {
     },
     "moe": {
         "kvb_route_top": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+        "kvb_route_top_scores": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+        "kvb_grouped_gemm_act": [_c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
+                                 _c_int, _c_int, _c_int, _c_float, _c_void_p],
+        "kvb_routed_combine_base": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
         "kvb_routed_plan": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
         "kvb_grouped_gemm": [_c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
                              _c_int, _c_int, _c_int, _c_void_p],
@@ -231,6 +252,7 @@ class CudaKernels(KernelSet):
         self._attn_generic = _Library("attention_generic")
         self._gemm_simt = _Library("gemm_simt")
         self._latent = _Library("latent")
+        self._recurrent = _Library("recurrent")
         self._moe = _Library("moe")
         self._latent_flash = _Library("latent_flash")
         self._gemm_grouped = _Library("gemm_grouped")
@@ -468,17 +490,35 @@ class CudaKernels(KernelSet):
                                                  _ptr(out), _ptr(rows), n_out, H, float(eps), self._stream()),
                "add_rmsnorm")
 
-    def silu_mul(self, gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
+    GATED_ACTIVATIONS = {"silu": 0, "clamped_swiglu": 1}
+
+    def silu_mul(self, gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False, activation: str = "silu",
+                 limit: float = 0.0) -> None:
+        """out = act(gate, up) of the two halves (or interleaved eights) of `gate_up`: "silu": silu(g) u;
+        "clamped_swiglu": g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit)."""
         T, I = out.shape
         self._count("silu_mul")
-        _check(self._elementwise.kvb_silu_mul(_dtype_code(out.dtype), _ptr(gate_up), _ptr(out), T, I,
-                                              1 if interleaved else 0, self._stream()), "silu_mul")
+        if activation == "silu":
+            _check(self._elementwise.kvb_silu_mul(_dtype_code(out.dtype), _ptr(gate_up), _ptr(out), T, I,
+                                                  1 if interleaved else 0, self._stream()), "silu_mul")
+            return
+        if activation not in self.GATED_ACTIVATIONS:
+            raise KernelError(f"silu_mul: activation '{activation}' is not built")
+        _check(self._elementwise.kvb_gated_act(_dtype_code(out.dtype), _ptr(gate_up), _ptr(out), T, I, 1 if interleaved else 0,
+                                               self.GATED_ACTIVATIONS[activation], float(limit), self._stream()), "gated_act")
 
-    def gate_up_act(self, x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, workspace, interleaved: bool) -> None:
-        """out[M, I] = silu(x Wg^T) * (x Wu^T); `w_gate_up` [2 I, K] holds gate and up rows one after the
-        other, or interleaved in eights (see csrc/gemm_skinny.cu)."""
+    def gate_up_act(self, x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, workspace, interleaved: bool,
+                    activation: str = "silu", limit: float = 0.0) -> None:
+        """out[M, I] = act(x Wg^T, x Wu^T) (see `silu_mul`); `w_gate_up` [2 I, K] holds gate and up rows one after the
+        other, or interleaved in eights (see csrc/gemm_skinny.cu).  The products with the activation in their epilogue
+        are built for silu; other activations take the product and the activation kernel."""
         M, K = x.shape
         I = out.shape[1]
+        if activation != "silu":
+            gate_up = workspace.buffer("ffn.gate_up", (M, 2 * I), out.dtype)
+            self.linear(x, w_gate_up, gate_up)
+            self.silu_mul(gate_up, out, interleaved, activation, limit)
+            return
         if interleaved and self._skinny(x.dtype, M, K, 2 * I):
             self._count("gemm_skinny")
             _check(self._gemm_skinny.kvb_gemm_skinny(_dtype_code(out.dtype), 1, _ptr(x), _ptr(w_gate_up), _ptr(None),
@@ -565,11 +605,24 @@ class CudaKernels(KernelSet):
 
     def qkv_rope_append(self, qkv: torch.Tensor, bias: Optional[torch.Tensor], cos: Optional[torch.Tensor],
                         sin: Optional[torch.Tensor], batch: StepBatch, kv: PagedKVView, q_out: torch.Tensor,
-                        num_heads: int) -> None:
+                        num_heads: int, q_norm: Optional[torch.Tensor] = None, k_norm: Optional[torch.Tensor] = None,
+                        norm_eps: float = 0.0) -> None:
+        """`q_norm` / `k_norm` (float32 [head_dim]): queries and keys are divided by their root mean square per head and
+        multiplied by these before the rotation.  Values may have another size than keys (`kv.spec.v_head_dim`), and rows
+        of `qkv` may carry further columns after [q | k | v]."""
         T = qkv.shape[0]
         spec = kv.spec
         rot_half = 0 if cos is None else cos.shape[1]
         table_len = 0 if cos is None else cos.shape[0]
+        if q_norm is not None or spec.v_head_dim != spec.head_dim or qkv.shape[1] != (num_heads + 2 * spec.num_kv_heads) * spec.head_dim:
+            self._count("norm_rope_append")
+            _check(self._rope.kvb_qkv_norm_rope_append(
+                _dtype_code(qkv.dtype), _ptr(qkv), qkv.shape[1], _ptr(bias), _ptr(q_norm), _ptr(k_norm), float(norm_eps), _ptr(cos),
+                _ptr(sin), rot_half, table_len, _ptr(batch.positions), _ptr(batch.row_segment), _ptr(kv.block_table),
+                kv.block_table.shape[1], _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(q_out), T, num_heads, spec.num_kv_heads,
+                spec.head_dim, spec.v_head_dim, kv.page_size, 1 if kv.writes else 0, _ptr(self.error_word), self._stream()),
+                "qkv_norm_rope_append")
+            return
         self._count("rope_append")
         _check(self._rope.kvb_qkv_rope_append(
             _dtype_code(qkv.dtype), _ptr(qkv), _ptr(bias), _ptr(cos), _ptr(sin), rot_half, table_len,
@@ -639,6 +692,14 @@ class CudaKernels(KernelSet):
         spec = kv.spec
         D, Hkv = spec.head_dim, spec.num_kv_heads
         plan = batch.plans.get(PagedAttentionPlanner.name)
+        if spec.v_head_dim != D:
+            # Values of another size than keys: the generic kernel, which takes any two sizes.
+            self._count("attention_generic")
+            _check(self._attn_generic.kvb_paged_attention_kv(
+                _dtype_code(q.dtype), _ptr(q), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table), kv.block_table.shape[1],
+                _ptr(batch.positions), _ptr(batch.row_segment), _ptr(out), T, num_heads, Hkv, D, spec.v_head_dim, kv.page_size,
+                spec.window or 0, float(scale), _ptr(self.error_word), self._stream()), "paged_attention")
+            return
         if (self.flash_attention and q.dtype == torch.bfloat16 and D % 16 == 0 and D <= 128 and num_heads // Hkv <= 16
                 and workspace is not None and plan is not None):
             lib = self._flash_library(D)
@@ -811,22 +872,36 @@ class CudaKernels(KernelSet):
             _ptr(batch.row_segment), _ptr(out), T, num_heads, spec.num_kv_heads, spec.head_dim, value_dim, kv.page_size,
             spec.window or 0, float(scale), _ptr(self.error_word), self._stream()), "latent_attention")
 
-    def route_top(self, logits: torch.Tensor, chosen: torch.Tensor, share: torch.Tensor) -> None:
-        """chosen[t] = the chosen.shape[1] experts with the largest logits[t] (float32), share[t] = softmax over those."""
+    def route_top(self, logits: torch.Tensor, chosen: torch.Tensor, share: torch.Tensor, scores: str = "chosen") -> None:
+        """chosen[t] = the chosen.shape[1] experts with the largest logits[t] (float32); share[t] = softmax over those
+        (`scores` "chosen"), or the softmax over all experts at the chosen ones, as it is ("all")."""
         T, E = logits.shape
         self._count("route_top")
-        _check(self._moe.kvb_route_top(_ptr(logits), _ptr(chosen), _ptr(share), T, E, chosen.shape[1], self._stream()), "route_top")
+        if scores == "chosen":
+            _check(self._moe.kvb_route_top(_ptr(logits), _ptr(chosen), _ptr(share), T, E, chosen.shape[1], self._stream()), "route_top")
+        elif scores == "all":
+            _check(self._moe.kvb_route_top_scores(_ptr(logits), _ptr(chosen), _ptr(share), T, E, chosen.shape[1], 1, self._stream()),
+                   "route_top")
+        else:
+            raise KernelError(f"route_top: scores '{scores}' (chosen, all)")
 
     ROUTED_SMALL_PAIRS = 256      # up to this many (row, choice) pairs the grouped products use tiles of 16 rows, else of 64
 
     def routed_experts(self, x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor,
-                       share: torch.Tensor, out: torch.Tensor, activation: str, workspace) -> None:
-        """out[t] = sum_s share[t, s] * w_down[e] . act(w_up[e] . x[t]), e = chosen[t, s]; w_up [E, F, H], w_down [E, H, F]."""
-        if activation != "relu2":
+                       share: torch.Tensor, out: torch.Tensor, activation: str, workspace, limit: float = 0.0,
+                       base: Optional[torch.Tensor] = None) -> None:
+        """out[t] = base[t] + sum_s share[t, s] * w_down[e] . act(w_up[e] . x[t]), e = chosen[t, s]; w_down [E, H, F].
+        "relu2": w_up [E, F, H], act = relu(.)^2.  "clamped_swiglu": w_up [E, 2 F, H] with gate row i at 2 i and up row i
+        at 2 i + 1, act = g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit)."""
+        if activation not in ("relu2", "clamped_swiglu"):
             raise KernelError(f"routed_experts: activation '{activation}' is not built")
         T, H = x.shape
         E, F, _ = w_up.shape
         top = chosen.shape[1]
+        if activation == "clamped_swiglu" or base is not None:
+            self._routed_general(x, w_up, w_down, chosen, share, out, 2 if activation == "clamped_swiglu" else 1, float(limit), base,
+                                 workspace)
+            return
         pairs = T * top
         ws, i32 = workspace, torch.int32
         code, stream = _dtype_code(x.dtype), self._stream()
@@ -872,6 +947,105 @@ class CudaKernels(KernelSet):
                                           max_tiles, BM, H, F, 0, stream), "grouped_gemm (down)")
         self._count("routed_combine")
         _check(self._moe.kvb_routed_combine(code, _ptr(y), _ptr(place), _ptr(share), _ptr(out), T, top, H, stream), "routed_combine")
+
+    def _routed_general(self, x, w_up, w_down, chosen, share, out, act: int, limit: float, base, ws) -> None:
+        """The routed feed-forward with any of the grouped product's activations and an optional base: plan, product up
+        (rows gathered, activation in the epilogue), product down, combine - float32 on CUDA cores, bfloat16 on `mma.sync`."""
+        T, H = x.shape
+        E, N, _ = w_up.shape
+        F = N // 2 if act == 2 else N
+        top = chosen.shape[1]
+        pairs = T * top
+        i32 = torch.int32
+        code, stream = _dtype_code(x.dtype), self._stream()
+        BM = 16 if pairs <= self.ROUTED_SMALL_PAIRS else 64
+        max_tiles = -(-pairs // BM) + E
+        place = ws.buffer("moe.place", (pairs,), i32)
+        order = ws.buffer("moe.order", (pairs,), i32)
+        plan = ws.buffer("moe.plan", (4,), i32)
+        tiles = ws.buffer("moe.tiles", (max_tiles * 3,), i32)
+        hidden = ws.buffer("moe.act", (pairs, F), x.dtype)
+        y = ws.buffer("moe.y", (pairs, H), x.dtype)
+        self._count("routed_plan")
+        _check(self._moe.kvb_routed_plan(_ptr(chosen), pairs, E, BM, 0, _ptr(place), _ptr(order), _ptr(plan), _ptr(tiles), stream),
+               "routed_plan")
+        self._count("grouped_gemm")
+        _check(self._moe.kvb_grouped_gemm_act(code, _ptr(x), _ptr(order), top, _ptr(w_up), _ptr(hidden), _ptr(plan), _ptr(tiles),
+                                              max_tiles, BM, N, H, act, limit, stream), "grouped_gemm (up)")
+        self._count("grouped_gemm")
+        _check(self._moe.kvb_grouped_gemm_act(code, _ptr(hidden), _ptr(order), 0, _ptr(w_down), _ptr(y), _ptr(plan), _ptr(tiles),
+                                              max_tiles, BM, H, F, 0, 0.0, stream), "grouped_gemm (down)")
+        self._count("routed_combine")
+        _check(self._moe.kvb_routed_combine_base(code, _ptr(y), _ptr(place), _ptr(share), _ptr(base), _ptr(out), T, top, H, stream),
+               "routed_combine")
+
+    # ---- hashed pair embedding, gated heads, matrix-state mixers ---------------------------------------------
+    def bigram_embed(self, table: torch.Tensor, batch: StepBatch, previous: torch.Tensor, h: torch.Tensor, buckets: int,
+                     mul_prev: int, mul_cur: int, vocab: int) -> None:
+        """h[r] += table[(previous token * mul_prev + token * mul_cur) mod buckets], or table[buckets] at position 0; the
+        token before a segment's first row is previous[slot], which then becomes the segment's last token."""
+        T, W = h.shape
+        self._count("bigram_embed")
+        self.launches += 1
+        _check(self._recurrent.kvb_bigram_embed(
+            _dtype_code(table.dtype), _ptr(table), _ptr(batch.token_ids), _ptr(batch.token_src), _ptr(batch.last_tokens),
+            _ptr(batch.positions), _ptr(batch.row_segment), _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_slot),
+            _ptr(previous), _ptr(h), T, batch.num_segments, W, int(buckets), int(mul_prev), int(mul_cur), int(vocab),
+            self._stream()), "bigram_embed")
+
+    def head_gate(self, x: torch.Tensor, gate, num_heads: int, value_dim: int, scale: float, out: torch.Tensor,
+                  out_col: int = 0) -> None:
+        """out[t, out_col + h * Dv + d] = x[t, h * Dv + d] * sigmoid(g[t, col + h]) * scale; `gate` = (g, col) or None."""
+        T = x.shape[0]
+        g, col = gate if gate is not None else (None, 0)
+        if g is not None and g.dtype != x.dtype:
+            raise KernelError("head_gate: the gate and the rows differ in type")
+        self._count("head_gate")
+        _check(self._recurrent.kvb_head_gate(_dtype_code(x.dtype), _ptr(x), _ptr(g), 0 if g is None else g.shape[1], col, float(scale),
+                                             _ptr(out), out.shape[1], out_col, T, num_heads, value_dim, self._stream()), "head_gate")
+
+    def head_norm_gate(self, o: torch.Tensor, weight: torch.Tensor, eps: float, gate, activation: str, scale: float,
+                       out: torch.Tensor, out_col: int, num_heads: int, value_dim: int) -> None:
+        """out[t, out_col + h * Dv + d] = o[t, h, d] / sqrt(mean_d o[t, h, :]^2 + eps) * w * act(g[t, col + h * Dv + d]) * scale;
+        o and g float32, `weight` of Dv numbers (all heads) or H * Dv, act "silu" or "sigmoid", `gate` = (g, col)."""
+        T = o.shape[0]
+        g, col = gate
+        if o.dtype != torch.float32 or g.dtype != torch.float32:
+            raise KernelError("head_norm_gate takes float32 rows")
+        if weight.numel() not in (value_dim, num_heads * value_dim):
+            raise KernelError("head_norm_gate: the weight fits neither one head nor all")
+        self._count("head_norm_gate")
+        _check(self._recurrent.kvb_head_norm_gate(
+            _dtype_code(out.dtype), _ptr(o), _ptr(weight), 1 if weight.numel() != value_dim else 0, float(eps), _ptr(g), g.shape[1],
+            col, {"silu": 0, "sigmoid": 1}[activation], float(scale), _ptr(out), out.shape[1], out_col, T, num_heads, value_dim,
+            self._stream()), "head_norm_gate")
+
+    def _scan(self, mode: int, proj, q_col, k_col, v_col, gate, g0, g1, p0, q_scale, floor, batch, memory, normalizer, maximum, out,
+              H, D, Dv) -> None:
+        if proj.dtype != torch.float32 or gate.dtype != torch.float32 or out.dtype != torch.float32 or memory.dtype != torch.float32:
+            raise KernelError("the matrix-state scan takes float32 rows and states")
+        if tuple(memory.shape[1:]) != (H, Dv, D):
+            raise KernelError(f"the matrix-state scan wants states [slots, {H}, {Dv}, {D}], got {tuple(memory.shape)}")
+        self._count("matrix_state_scan")
+        _check(self._recurrent.kvb_matrix_state_scan(
+            mode, _ptr(proj), proj.shape[1], q_col, k_col, v_col, _ptr(gate), gate.shape[1], g0, g1, float(p0), float(q_scale),
+            float(floor), _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_slot), _ptr(memory), _ptr(normalizer),
+            _ptr(maximum), _ptr(out), batch.num_segments, H, D, Dv, self._stream()), "matrix_state_scan")
+
+    def gated_linear_scan(self, proj: torch.Tensor, cols, z: torch.Tensor, tau: float, q_scale: float, batch: StepBatch,
+                          memory: torch.Tensor, out: torch.Tensor, H: int, D: int, Dv: int) -> None:
+        """Per segment, from and into memory[slot] ([H, Dv, D], float32): S = diag(a_t) S + k_t v_t^T, out_t = S^T (q_t q_scale),
+        a_t = sigmoid(z_t)^(1 / tau) per key channel; q, k, v at columns `cols` of the float32 rows `proj`."""
+        self._scan(0, proj, cols[0], cols[1], cols[2], z, 0, 0, tau, q_scale, 0.0, batch, memory, None, None, out, H, D, Dv)
+
+    def matrix_memory_scan(self, proj: torch.Tensor, cols, cap: float, q_scale: float, floor: float, batch: StepBatch,
+                           memory: torch.Tensor, normalizer: torch.Tensor, maximum: torch.Tensor, out: torch.Tensor, H: int, D: int,
+                           Dv: int) -> None:
+        """Per segment, from and into (memory, normalizer, maximum)[slot]: i = cap tanh(x_i / cap), f = logsigmoid(cap tanh(x_f / cap)),
+        m' = max(f + m, i), S = e^{f + m - m'} S + e^{i - m'} k v^T, n likewise with k, out = S^T q / (max(|n . q|, e^{-m'}) + floor);
+        q, k, v and the gates' pre-activations x_i, x_f (one per head) at columns `cols` of `proj`."""
+        self._scan(1, proj, cols[0], cols[1], cols[2], proj, cols[3], cols[4], cap, q_scale, floor, batch, memory, normalizer, maximum,
+                   out, H, D, Dv)
 
     def sample(self, logits: torch.Tensor, temperature: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor,
                out: torch.Tensor, scratch_val: torch.Tensor, scratch_idx: torch.Tensor) -> None:

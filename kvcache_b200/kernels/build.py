@@ -31,6 +31,7 @@ MODULES: Dict[str, dict] = {
     "attention_generic": {"src": "attention_generic.cu", "deps": ["common.cuh"]},
     "gemm_simt": {"src": "gemm_simt.cu", "deps": ["common.cuh"]},
     "latent": {"src": "latent.cu", "deps": ["common.cuh", "mma_tile.cuh"]},
+    "recurrent": {"src": "recurrent.cu", "deps": ["common.cuh"]},
     "moe": {"src": "moe.cu", "deps": ["common.cuh", "mma_tile.cuh"]},
     "latent_flash": {"src": "latent_flash.cu", "deps": ["common.cuh"]},
     "gemm_grouped": {"src": "gemm_grouped.cu", "deps": ["common.cuh", "tc_common.cuh"]},

@@ -47,7 +47,8 @@ def _attention_bytes(batch, kv, num_heads: int) -> int:
 class KernelTiming:
     OPERATORS = ("embed", "add_rmsnorm", "silu_mul", "gate_up_act", "linear", "qkv_rope_append", "rope_append_attention",
                  "paged_attention", "sample", "norm_add_rmsnorm", "latent_norm_rope_append", "head_linear", "latent_attention",
-                 "route_top", "routed_experts")
+                 "route_top", "routed_experts", "bigram_embed", "head_gate", "head_norm_gate", "gated_linear_scan",
+                 "matrix_memory_scan")
 
     def __init__(self, kernels, hold_ms: float = 4.0):
         self.kernels = kernels
