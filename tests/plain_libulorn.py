@@ -221,3 +221,11 @@ def logits_of(config: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int]) -
     eps = float(config["norm"]["eps"])
     x = residual_streams(config, w, tokens)[-1]
     return linear(unit(x, eps) * w["final.norm"], w["head"])
+
+
+def greedy_generate(config: dict, w: Dict[str, torch.Tensor], prompt: Sequence[int], new_tokens: int) -> List[int]:
+    tokens, out = list(prompt), []
+    for _ in range(new_tokens):
+        out.append(int(torch.argmax(logits_of(config, w, tokens)[-1])))
+        tokens.append(out[-1])
+    return out
