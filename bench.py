@@ -1,7 +1,7 @@
 """Benchmark of kvcache_b200: decode tokens a second of the Qwen2.5-0.5B shape on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --design kakipel [--sizes 0.5B-like,3B-like]     (another workload, see `run_design`; the default stays as it is)
+    python bench.py --design kakipel|libulorn [--sizes 0.5B-like,3B-like]     (another workload, see `run_design`; the default stays as it is)
 
 One JSON line on standard output.  `value`: decoded tokens a second at batch 8 and the
 benchmark context (device-timed decode steps through the engine's step function and device
@@ -441,6 +441,32 @@ def design_sizes():
     return out
 
 
+def libulorn_sizes():
+    """Layer sizes that resemble real models, as (name, {architecture: config}): a Libulorn model of four layers (parallel,
+    matrix memory, parallel, matrix memory; every layer with a routed feed-forward whose chosen experts and shared expert
+    together have as many active weights per token as the dense feed-forward of that width), beside the Kakipel and Qwen2
+    models of `design_sizes` at equal width, layer count, feed-forward width and vocabulary.  In the sizes called
+    "wide-values" a head's values are twice as wide as its keys (half as many heads), as in the design's own models."""
+    out = []
+    others = {name: (kaki, qwen) for name, kaki, qwen in design_sizes()}
+    for name, like, width, heads, kv_heads, dim, vdim, r_heads, r_dim, r_vdim, ff, experts, top, vocab in (
+            ("0.5B-like", "0.5B-like", 896, 14, 2, 64, 64, 7, 64, 128, 4864, 16, 2, 32768),
+            ("0.5B-like-wide-values", "0.5B-like", 896, 7, 1, 64, 128, 7, 64, 128, 4864, 16, 2, 32768),
+            ("3B-like", "3B-like", 2048, 16, 2, 128, 128, 8, 128, 256, 11008, 32, 4, 32768)):
+        left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "mask": {"size": 1024},
+                "rot": {"base": 10000.0, "dims": dim // 2, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 2048}}}
+        right = {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "tau": 16.0, "decay_rank": 16}
+        mlp = {"kind": "moe", "expert": {"ff": ff // (2 * top) // 16 * 16, "limit": 7.0}, "router": {"experts": experts, "top": top},
+               "shared": {"ff": ff // 2, "limit": 7.0}}
+        parallel = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}, "mlp": mlp}
+        memory = {"type": "mlstm", "mixer": {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "gate_cap": 15.0}, "mlp": mlp}
+        lib = {"architecture": "Libulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+               "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+               "layers": [parallel, memory, parallel, memory], "initializer_range": 0.02}
+        out.append((name, {"libulorn": lib, "kakipel": others[like][0], "qwen2": others[like][1]}))
+    return out
+
+
 def _write_design_folder(tmp, tag, config):
     import torch
     import kvcache_b200  # noqa: F401
@@ -533,18 +559,28 @@ def _time_classes(folder, peaks, mode, batch, context, tokens, repeats=3):
 
 
 def run_design(args) -> int:
-    """`--design kakipel`: decode and prefill throughput of the Kakipel architecture at sizes that resemble real models'
+    """`--design kakipel | libulorn`: decode and prefill throughput of that architecture at sizes that resemble real models'
     layers, beside the Qwen2 architecture at equal width, layer runs, feed-forward width and vocabulary (random weights,
     random cache contents for decode), and every class of kernel of one step of each against its roofline."""
     peaks = load_peaks()
     clocks = ClockSampler().start()
     results = []
+    if args.design == "libulorn":
+        sizes, beside = libulorn_sizes(), "Libulorn beside Kakipel and Qwen2"
+    else:
+        sizes, beside = [(name, {"kakipel": kaki, "qwen2": qwen}) for name, kaki, qwen in design_sizes()], "Kakipel beside Qwen2"
+    done = {}
     with tempfile.TemporaryDirectory() as tmp:
-        for name, kaki, qwen in design_sizes():
+        for name, configs in sizes:
             if args.sizes and name not in args.sizes.split(","):
                 continue
-            entry = {"size": name, "width": kaki["width"], "layer_runs": 4, "vocab": kaki["vocab"]}
-            for arch, config in (("kakipel", kaki), ("qwen2", qwen)):
+            first = next(iter(configs.values()))
+            entry = {"size": name, "width": first["width"], "layer_runs": 4, "vocab": first["vocab"]}
+            for arch, config in configs.items():
+                key = json.dumps(config, sort_keys=True)
+                if key in done:                          # the same model beside two sizes of the design: measured once
+                    entry[arch] = done[key]
+                    continue
                 folder = _write_design_folder(tmp, f"{arch}_{name}", config)
                 run = time_decode(folder, args.batch, args.context, args.steps, args.warmup, clocks, f"{arch} {name} decode")
                 prefill_ms = _time_prefill_plain(folder, PREFILL_TOKENS, clocks, f"{arch} {name} prefill")
@@ -556,11 +592,11 @@ def run_design(args) -> int:
                 if not args.skip_kernels:
                     item["decode_kernels"] = _time_classes(folder, peaks, "decode", args.batch, args.context, PREFILL_TOKENS)
                     item["prefill_kernels"] = _time_classes(folder, peaks, "prefill", args.batch, args.context, PREFILL_TOKENS)
-                entry[arch] = item
+                entry[arch] = done[key] = item
             results.append(entry)
     clocks.stop()
     print(json.dumps({"metric": f"decode tok/s at batch {args.batch}, context {args.context}, and prefill tok/s of one {PREFILL_TOKENS}-token prompt: "
-                                "Kakipel beside Qwen2 at equal sizes", "impl": "ours", "design": "kakipel", "dtype": "bf16",
+                                f"{beside} at equal sizes", "impl": "ours", "design": args.design, "dtype": "bf16",
                       "data": "synthetic", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "peaks": peaks, "sizes": results,
                       "clocks": {"how": clocks.how, "regions": clocks.regions}}))
     return 0
@@ -653,7 +689,7 @@ def main() -> int:
     parser.add_argument("--skip-prefill", action="store_true")
     parser.add_argument("--skip-kernels", action="store_true")
     parser.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for profilers)")
-    parser.add_argument("--design", default=None, choices=["kakipel"],
+    parser.add_argument("--design", default=None, choices=["kakipel", "libulorn"],
                         help="instead of the default workload: this architecture beside Qwen2 at equal sizes (decode, prefill, kernels)")
     parser.add_argument("--sizes", default="", help="with --design: the sizes to run, with commas between them (default: all)")
     args = parser.parse_args()

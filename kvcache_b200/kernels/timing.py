@@ -106,6 +106,23 @@ class KernelTiming:
             used = min(w_up.shape[0], chosen.numel())          # experts a step can touch at most
             per_expert = (w_up[0].numel() + w_down[0].numel()) * w_up.element_size()
             return f"routed_experts {w_up.shape[0]}x{w_up.shape[1]}x{w_up.shape[2]}", used * per_expert + _numel_bytes(x) + _numel_bytes(out)
+        if name == "bigram_embed":
+            h, table = args[3], args[0]
+            return name, h.numel() * (8 + table.element_size())
+        if name == "head_gate":
+            return name, 2 * _numel_bytes(args[0])
+        if name == "head_norm_gate":
+            o, out, H, Dv = args[0], args[6], args[8], args[9]
+            return name, 2 * _numel_bytes(o) + o.shape[0] * H * Dv * out.element_size()
+        if name in ("gated_linear_scan", "matrix_memory_scan"):
+            # The rows' q, k, decay (or gates) and v in, the read-outs out, and every segment's state in and out.
+            if name == "gated_linear_scan":
+                proj, batch, memory, out, H, D, Dv = args[0], args[5], args[6], args[7], args[8], args[9], args[10]
+                per_row = 3 * H * D + 2 * H * Dv
+            else:
+                proj, batch, memory, out, H, D, Dv = args[0], args[5], args[6], args[9], args[10], args[11], args[12]
+                per_row = 2 * H * D + 2 * H * Dv + 2 * H
+            return f"{name} {H}x{D}x{Dv}", 4 * (proj.shape[0] * per_row + 2 * batch.num_segments * H * D * Dv)
         return name, 0
 
     @staticmethod
@@ -136,8 +153,12 @@ class KernelTiming:
             batch, kv, heads = args[4], args[5], args[7]
             return 4 * heads * kv.spec.head_dim * cls._keys_seen(batch)
         if name == "routed_experts":
-            x, w_up, chosen = args[0], args[1], args[3]
-            return 2 * chosen.numel() * 2 * w_up.shape[1] * w_up.shape[2]
+            x, w_up, w_down, chosen = args[0], args[1], args[2], args[3]
+            return 2 * chosen.numel() * (w_up.shape[1] * w_up.shape[2] + w_down.shape[1] * w_down.shape[2])
+        if name == "gated_linear_scan":
+            return 4 * args[0].shape[0] * args[8] * args[9] * args[10]          # per row and state element: decay-and-add, read-out
+        if name == "matrix_memory_scan":
+            return 4 * args[0].shape[0] * args[10] * args[11] * args[12]
         return 0
 
     # ---- switching on and off -------------------------------------------------------------------------

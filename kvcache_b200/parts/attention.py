@@ -105,6 +105,17 @@ class GQAAttention(Mixer):
         self.w_qkv_paired = self.b_qkv_paired = None
         self._can_pair = self.plain and self.dtype == torch.bfloat16 and self.head_dim % 16 == 0 and device.type == "cuda"
 
+    def _pair_rows(self, kernels) -> bool:
+        """Makes the row-paired copy of the q/k/v weight and bias if the kernel set can use one."""
+        rotation = self.position.rotation() if self.position is not None else None
+        whole = rotation is None or rotation.cos.shape[1] * 2 == self.head_dim
+        if self.w_qkv_paired is None and self._can_pair and whole and hasattr(kernels, "pair_rotation_rows"):
+            order = kernels.pair_rotation_rows(self.num_heads + 2 * self.num_kv_heads, self.head_dim).to(self.w_qkv.device)
+            self.w_qkv_paired = self.w_qkv.index_select(0, order).contiguous()
+            if self.b_qkv is not None:
+                self.b_qkv_paired = self.b_qkv.index_select(0, order).contiguous()
+        return self.w_qkv_paired is not None
+
     def weight_bytes(self) -> int:
         n = self.w_qkv.numel() * self.w_qkv.element_size() + self.w_o.numel() * self.w_o.element_size()
         return n + (self.b_qkv.numel() * 4 if self.b_qkv is not None else 0)
