@@ -13,6 +13,13 @@
 // multiply-adds per held number, one shuffle tree per column, and no barrier.  A column's sum over the key channels
 // is taken in one order (lane-local over l + 32 i, then the xor tree), whatever the step holds: a token's result is
 // bit for bit the same in a prompt, a portion or alone.  State layout: [slot, head, value channel, key channel].
+//
+// Long segments are cut into chunks of L tokens that run side by side, in three launches: (1) every chunk but a
+// segment's last is scanned from an empty state and leaves its end state and its total decay in scratch; (2) per
+// segment, the chunks' start states follow one from the other (start[c + 1] = decay[c] start[c] + local[c], for the
+// exponential gates with their maxima: m' = max(F + m, m_local), weights e^{F + m - m'} and e^{m_local - m'}); (3) every
+// chunk is scanned again from its start state, now with read-outs, and a segment's last chunk leaves the state in the
+// slot.  The arithmetic per token is the same as in one piece; the start states differ from it by float32 rounding.
 #include "common.cuh"
 
 enum { SCAN_CHANNEL_DECAY = 0, SCAN_EXP_GATES = 1 };
@@ -25,35 +32,80 @@ __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - l
 //                     o = S'^T q / (max(|n' . q|, e^{-m'}) + floor).  n: [slot, head, key channel], m: [slot, head].
 // grid (column blocks, heads, segments); the exponential-gate form takes one block per head (its n and m are read by
 // every warp at the start and written by the first at the end, with a barrier in between).
-template <int MODE, int RPL, int CPW>
+// Scratch of the chunked form; chunk ids count the chunks of all segments in the order of the segments.
+struct ScanChunks {
+    int L, S;              // tokens in a chunk; segments in the step
+    float* local_S;        // [chunk, H, Dv, D]   end state of the chunk scanned from an empty state
+    float* local_vec;      // [chunk, H, D]       channel decay: the product of the chunk's decays; exponential gates: its normaliser
+    float* local_F;        // [chunk, H]          exponential gates: the sum of the chunk's log forget gates
+    float* local_m;        // [chunk, H]          exponential gates: the chunk's maximum from an empty state
+    float* start_S;        // [chunk, H, Dv, D]   state before the chunk's first token
+    float* start_vec;      // [chunk, H, D]       exponential gates: the normaliser there
+    float* start_m;        // [chunk, H]          exponential gates: the maximum there
+};
+
+// Which (segment, chunk of it) the chunk id is; false beyond the step's last chunk.
+__device__ __forceinline__ bool find_chunk(int id, const ScanChunks& ch, const int* seg_q_len, int& seg, int& index, int& count,
+                                           int& first_id) {
+    int at = 0;
+    for (int s = 0; s < ch.S; ++s) {
+        const int nc = (seg_q_len[s] + ch.L - 1) / ch.L;
+        if (id < at + nc) {
+            seg = s; index = id - at; count = nc; first_id = at;
+            return true;
+        }
+        at += nc;
+    }
+    return false;
+}
+
+enum { SCAN_WHOLE = 0, SCAN_LOCAL = 1, SCAN_FROM_START = 3 };
+
+// PASS: SCAN_WHOLE - grid z counts segments, from and into the slots.  SCAN_LOCAL / SCAN_FROM_START - grid z counts
+// chunks (launches (1) and (3) of the chunked form).
+template <int MODE, int RPL, int CPW, int PASS>
 __global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 1024 : 256) matrix_state_scan_kernel(
     const float* __restrict__ proj, int P, int q_col, int k_col, int v_col, const float* __restrict__ gate, int gate_stride,
     int g0, int g1, float p0, float q_scale, float floor_, const int* __restrict__ seg_q_start,
     const int* __restrict__ seg_q_len, const int* __restrict__ seg_slot, float* __restrict__ memory,
-    float* __restrict__ normalizer, float* __restrict__ maximum, float* __restrict__ out, int H, int D, int Dv) {
+    float* __restrict__ normalizer, float* __restrict__ maximum, float* __restrict__ out, int H, int D, int Dv, ScanChunks ch) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-    const int h = blockIdx.y, seg = blockIdx.z;
+    const int h = blockIdx.y;
     const int c0 = (blockIdx.x * warps + warp) * CPW;
-    const int r0 = seg_q_start[seg], n_rows = seg_q_len[seg], slot = seg_slot[seg];
+    int seg = blockIdx.z, chunk = 0, chunks = 1, first_id = 0;
+    if (PASS != SCAN_WHOLE && !find_chunk(blockIdx.z, ch, seg_q_len, seg, chunk, chunks, first_id)) return;
+    const bool last_chunk = chunk == chunks - 1;
+    if (PASS == SCAN_LOCAL && last_chunk) return;              // nobody starts from its end
+    int r0 = seg_q_start[seg], n_rows = seg_q_len[seg];
+    const int slot = seg_slot[seg];
+    if (PASS != SCAN_WHOLE) {
+        r0 += chunk * ch.L;
+        n_rows = min(ch.L, n_rows - chunk * ch.L);
+    }
     pdl_wait();
     pdl_launch_dependents();
-    float S[CPW][RPL], nz[RPL], m = 0.f;
+    float S[CPW][RPL], nz[RPL], total[RPL], m = 0.f, F = 0.f;
     float* mem = memory + ((size_t)slot * H + h) * Dv * D;
+    const size_t cid = (size_t)blockIdx.z * H + h;             // (chunk id, head) in the scratch arrays
+    const float* from = PASS == SCAN_FROM_START ? ch.start_S + cid * Dv * D : mem;
 #pragma unroll
     for (int c = 0; c < CPW; ++c)
 #pragma unroll
         for (int i = 0; i < RPL; ++i) {
             const int d = lane + 32 * i;
-            S[c][i] = (c0 + c < Dv && d < D) ? mem[(size_t)(c0 + c) * D + d] : 0.f;
+            S[c][i] = (PASS != SCAN_LOCAL && c0 + c < Dv && d < D) ? from[(size_t)(c0 + c) * D + d] : 0.f;
         }
+#pragma unroll
+    for (int i = 0; i < RPL; ++i) total[i] = 1.f;
     if (MODE == SCAN_EXP_GATES) {
+        const float* n_from = PASS == SCAN_FROM_START ? ch.start_vec + cid * D : normalizer + ((size_t)slot * H + h) * D;
 #pragma unroll
         for (int i = 0; i < RPL; ++i) {
             const int d = lane + 32 * i;
-            nz[i] = d < D ? normalizer[((size_t)slot * H + h) * D + d] : 0.f;
+            nz[i] = (PASS != SCAN_LOCAL && d < D) ? n_from[d] : 0.f;
         }
-        m = maximum[(size_t)slot * H + h];
-        __syncthreads();                      // every warp has read n and m before the first may write them
+        m = PASS == SCAN_LOCAL ? -FLT_MAX : PASS == SCAN_FROM_START ? ch.start_m[cid] : maximum[(size_t)slot * H + h];
+        if (PASS == SCAN_WHOLE) __syncthreads();   // every warp has read n and m before the first may write them
     }
     // The rows of the next token are fetched while this one is computed: none of them depends on the state.
     float q[RPL], k[RPL], a[RPL], v[CPW], gi = 0.f, gf = 0.f;
@@ -86,9 +138,13 @@ __global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 1024 : 256) matrix_st
         float keep = 1.f, take = 1.f, denom = 1.f;
         if (MODE == SCAN_CHANNEL_DECAY) {
 #pragma unroll
-            for (int i = 0; i < RPL; ++i) ac[i] = expf(log_sigmoid(ac[i]) / p0);
+            for (int i = 0; i < RPL; ++i) {
+                ac[i] = expf(log_sigmoid(ac[i]) / p0);
+                if (PASS == SCAN_LOCAL) total[i] *= ac[i];
+            }
         } else {
             const float li = p0 * tanhf(gic / p0), lf = log_sigmoid(p0 * tanhf(gfc / p0));
+            if (PASS == SCAN_LOCAL) F += lf;
             const float m_new = fmaxf(lf + m, li);
             keep = expf(lf + m - m_new);
             take = expf(li - m_new);
@@ -99,7 +155,17 @@ __global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 1024 : 256) matrix_st
                 nz[i] = keep * nz[i] + take * kc[i];
                 part += nz[i] * qc[i];
             }
-            denom = fmaxf(fabsf(warp_sum(part)), expf(-m_new)) + floor_;
+            if (PASS != SCAN_LOCAL) denom = fmaxf(fabsf(warp_sum(part)), expf(-m_new)) + floor_;
+        }
+        if (PASS == SCAN_LOCAL) {                 // the state only
+#pragma unroll
+            for (int c = 0; c < CPW; ++c)
+#pragma unroll
+                for (int i = 0; i < RPL; ++i) {
+                    if (MODE == SCAN_CHANNEL_DECAY) S[c][i] = ac[i] * S[c][i] + kc[i] * vc[c];
+                    else S[c][i] = keep * S[c][i] + take * (kc[i] * vc[c]);
+                }
+            continue;
         }
         float o[CPW];
 #pragma unroll
@@ -119,49 +185,148 @@ __global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 1024 : 256) matrix_st
             if (lane == c && c0 + c < Dv) out[(size_t)r * H * Dv + h * Dv + c0 + c] = o[c];
     }
     if (n_rows <= 0) return;
+    if (PASS == SCAN_FROM_START && !last_chunk) return;        // only a segment's last chunk leaves the state in the slot
+    float* to = PASS == SCAN_LOCAL ? ch.local_S + cid * Dv * D : mem;
 #pragma unroll
     for (int c = 0; c < CPW; ++c)
 #pragma unroll
         for (int i = 0; i < RPL; ++i) {
             const int d = lane + 32 * i;
-            if (c0 + c < Dv && d < D) mem[(size_t)(c0 + c) * D + d] = S[c][i];
+            if (c0 + c < Dv && d < D) to[(size_t)(c0 + c) * D + d] = S[c][i];
         }
-    if (MODE == SCAN_EXP_GATES && blockIdx.x == 0 && warp == 0) {
+    if (blockIdx.x != 0 || warp != 0) return;
+    if (MODE == SCAN_CHANNEL_DECAY) {
+        if (PASS == SCAN_LOCAL)
 #pragma unroll
-        for (int i = 0; i < RPL; ++i) {
-            const int d = lane + 32 * i;
-            if (d < D) normalizer[((size_t)slot * H + h) * D + d] = nz[i];
-        }
-        if (lane == 0) maximum[(size_t)slot * H + h] = m;
+            for (int i = 0; i < RPL; ++i) {
+                const int d = lane + 32 * i;
+                if (d < D) ch.local_vec[cid * D + d] = total[i];
+            }
+        return;
     }
+    float* n_to = PASS == SCAN_LOCAL ? ch.local_vec + cid * D : normalizer + ((size_t)slot * H + h) * D;
+#pragma unroll
+    for (int i = 0; i < RPL; ++i) {
+        const int d = lane + 32 * i;
+        if (d < D) n_to[d] = nz[i];
+    }
+    if (lane == 0) {
+        if (PASS == SCAN_LOCAL) {
+            ch.local_m[cid] = m;
+            ch.local_F[cid] = F;
+        } else {
+            maximum[(size_t)slot * H + h] = m;
+        }
+    }
+}
+
+// Launch (2) of the chunked form: one block per (head, segment) walks the segment's chunks in order.
+template <int MODE>
+__global__ void scan_chunk_starts_kernel(const int* __restrict__ seg_q_len, const int* __restrict__ seg_slot,
+                                         const float* __restrict__ memory, const float* __restrict__ normalizer,
+                                         const float* __restrict__ maximum, int H, int D, int Dv, ScanChunks ch) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int h = blockIdx.x, seg = blockIdx.y;
+    int first = 0;
+    for (int s = 0; s < seg; ++s) first += (seg_q_len[s] + ch.L - 1) / ch.L;
+    const int chunks = (seg_q_len[seg] + ch.L - 1) / ch.L;
+    if (chunks <= 0) return;
+    const int slot = seg_slot[seg];
+    const size_t per = (size_t)Dv * D;
+    const float* mem = memory + ((size_t)slot * H + h) * per;
+    for (size_t e = threadIdx.x; e < per; e += blockDim.x) {
+        const int d = (int)(e % D);
+        float s = mem[e];
+        float m = MODE == SCAN_EXP_GATES ? maximum[(size_t)slot * H + h] : 0.f;
+        for (int c = 0; c < chunks; ++c) {
+            const size_t cid = (size_t)(first + c) * H + h;
+            ch.start_S[cid * per + e] = s;
+            if (c + 1 == chunks) break;
+            if (MODE == SCAN_CHANNEL_DECAY) {
+                s = ch.local_vec[cid * D + d] * s + ch.local_S[cid * per + e];
+            } else {
+                const float F = ch.local_F[cid], ml = ch.local_m[cid];
+                const float m1 = fmaxf(F + m, ml);
+                s = expf(F + m - m1) * s + expf(ml - m1) * ch.local_S[cid * per + e];
+                m = m1;
+            }
+        }
+    }
+    if (MODE == SCAN_EXP_GATES)
+        for (int d = threadIdx.x; d < D; d += blockDim.x) {
+            float n = normalizer[((size_t)slot * H + h) * D + d];
+            float m = maximum[(size_t)slot * H + h];
+            for (int c = 0; c < chunks; ++c) {
+                const size_t cid = (size_t)(first + c) * H + h;
+                ch.start_vec[cid * D + d] = n;
+                if (d == 0) ch.start_m[cid] = m;
+                if (c + 1 == chunks) break;
+                const float F = ch.local_F[cid], ml = ch.local_m[cid];
+                const float m1 = fmaxf(F + m, ml);
+                n = expf(F + m - m1) * n + expf(ml - m1) * ch.local_vec[cid * D + d];
+                m = m1;
+            }
+        }
 }
 
 template <int MODE, int RPL, int CPW>
 static void launch_scan(const float* proj, int P, int q_col, int k_col, int v_col, const float* gate, int gate_stride, int g0, int g1,
                         float p0, float q_scale, float floor_, const int* seg_q_start, const int* seg_q_len, const int* seg_slot,
-                        float* memory, float* normalizer, float* maximum, float* out, int S, int H, int D, int Dv, cudaStream_t stream) {
+                        float* memory, float* normalizer, float* maximum, float* out, int S, int H, int D, int Dv, ScanChunks ch,
+                        int max_chunks, cudaStream_t stream) {
     const int total_warps = (Dv + CPW - 1) / CPW;
     // The exponential-gate form: all of a head's columns in one block.  The other: blocks of up to 8 warps.
     const int warps = MODE == SCAN_EXP_GATES ? total_warps : (total_warps < 8 ? total_warps : 8);
-    dim3 grid((total_warps + warps - 1) / warps, H, S);
-    kvb_launch(matrix_state_scan_kernel<MODE, RPL, CPW>, grid, dim3(32 * warps), 0, stream, proj, P, q_col, k_col, v_col, gate,
-               gate_stride, g0, g1, p0, q_scale, floor_, seg_q_start, seg_q_len, seg_slot, memory, normalizer, maximum, out, H, D, Dv);
+    const int col_blocks = (total_warps + warps - 1) / warps;
+#define KVB_SCAN_PASS(PASS, Z)                                                                                                  \
+    kvb_launch(matrix_state_scan_kernel<MODE, RPL, CPW, PASS>, dim3(col_blocks, H, Z), dim3(32 * warps), 0, stream, proj, P, q_col, \
+               k_col, v_col, gate, gate_stride, g0, g1, p0, q_scale, floor_, seg_q_start, seg_q_len, seg_slot, memory, normalizer,  \
+               maximum, out, H, D, Dv, ch)
+    if (max_chunks <= 0) {
+        KVB_SCAN_PASS(SCAN_WHOLE, S);
+        return;
+    }
+    KVB_SCAN_PASS(SCAN_LOCAL, max_chunks);
+    kvb_launch(scan_chunk_starts_kernel<MODE>, dim3(H, S), dim3(256), 0, stream, seg_q_len, seg_slot, (const float*)memory,
+               (const float*)normalizer, (const float*)maximum, H, D, Dv, ch);
+    KVB_SCAN_PASS(SCAN_FROM_START, max_chunks);
+#undef KVB_SCAN_PASS
 }
 
 // proj: float32 [T, P] with q at q_col (H * D numbers), k at k_col, v at v_col (H * Dv).  `gate`: float32 rows of
 // stride gate_stride - per-channel decay logits at g0 (mode 0), or the two gates' pre-activations at g0 and g1 (mode 1).
+// `max_chunks` > 0: the chunked form with chunks of `chunk_len` tokens; `max_chunks` bounds the step's chunk count
+// (sum over segments of ceil(len / chunk_len)) and `scratch` holds that many times H * (2 Dv D + 2 D + 3) floats.
+// scratch floats: max_chunks * H * (2 * Dv * D + 2 * D + 3).
+
 KVB_API int kvb_matrix_state_scan(int mode, const float* proj, int P, int q_col, int k_col, int v_col, const float* gate,
                                   int gate_stride, int g0, int g1, float p0, float q_scale, float floor_, const int* seg_q_start,
                                   const int* seg_q_len, const int* seg_slot, float* memory, float* normalizer, float* maximum,
-                                  float* out, int S, int H, int D, int Dv, cudaStream_t stream) {
+                                  float* out, int S, int H, int D, int Dv, int chunk_len, int max_chunks, float* scratch,
+                                  cudaStream_t stream) {
     if (S <= 0) return KVB_OK;
     if (H < 1 || D < 1 || Dv < 1 || (mode != SCAN_CHANNEL_DECAY && mode != SCAN_EXP_GATES)) return KVB_ERR_SHAPE;
-    if (D > 256 || Dv > 256 || H > 65535 || S > 65535) return KVB_ERR_LIMIT;
+    if (D > 256 || Dv > 256 || H > 65535 || S > 65535 || max_chunks > 65535) return KVB_ERR_LIMIT;
+    if (max_chunks > 0 && (chunk_len < 1 || scratch == nullptr)) return KVB_ERR_SHAPE;
+    ScanChunks ch = {};
+    if (max_chunks > 0) {
+        const size_t states = (size_t)max_chunks * H * Dv * D, vecs = (size_t)max_chunks * H * D, ones = (size_t)max_chunks * H;
+        ch.L = chunk_len;
+        ch.S = S;
+        ch.local_S = scratch;
+        ch.start_S = ch.local_S + states;
+        ch.local_vec = ch.start_S + states;
+        ch.start_vec = ch.local_vec + vecs;
+        ch.local_F = ch.start_vec + vecs;
+        ch.local_m = ch.local_F + ones;
+        ch.start_m = ch.local_m + ones;
+    }
     const int rpl = D <= 32 ? 1 : D <= 64 ? 2 : D <= 128 ? 4 : 8;
     const int cpw = Dv <= 32 ? 1 : Dv <= 128 ? 4 : 8;
 #define KVB_SCAN(MODE, RPL, CPW)                                                                                              \
     launch_scan<MODE, RPL, CPW>(proj, P, q_col, k_col, v_col, gate, gate_stride, g0, g1, p0, q_scale, floor_, seg_q_start,     \
-                                seg_q_len, seg_slot, memory, normalizer, maximum, out, S, H, D, Dv, stream)
+                                seg_q_len, seg_slot, memory, normalizer, maximum, out, S, H, D, Dv, ch, max_chunks, stream)
 #define KVB_SCAN_CPW(MODE, RPL)                                                                                               \
     do {                                                                                                                      \
         if (cpw == 1) KVB_SCAN(MODE, RPL, 1); else if (cpw == 4) KVB_SCAN(MODE, RPL, 4); else KVB_SCAN(MODE, RPL, 8);         \

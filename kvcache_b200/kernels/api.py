@@ -103,7 +103,7 @@ _SIGNATURES = {
     "recurrent": {
         "kvb_matrix_state_scan": [_c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_float,
                                   _c_float, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
-                                  _c_int, _c_int, _c_int, _c_int, _c_void_p],
+                                  _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
         "kvb_head_norm_gate": [_c_int, _c_void_p, _c_void_p, _c_int, _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p,
                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
         "kvb_head_gate": [_c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -1020,32 +1020,45 @@ class CudaKernels(KernelSet):
             col, {"silu": 0, "sigmoid": 1}[activation], float(scale), _ptr(out), out.shape[1], out_col, T, num_heads, value_dim,
             self._stream()), "head_norm_gate")
 
+    # A step whose longest segment has at least SCAN_CHUNK_MIN_ROWS tokens scans its segments in chunks of SCAN_CHUNK tokens
+    # that run side by side (three launches, see csrc/recurrent.cu); below that a segment is one piece, and a token's
+    # result is bit for bit the same however the request was cut.
+    SCAN_CHUNK = 64
+    SCAN_CHUNK_MIN_ROWS = 256
+
     def _scan(self, mode: int, proj, q_col, k_col, v_col, gate, g0, g1, p0, q_scale, floor, batch, memory, normalizer, maximum, out,
-              H, D, Dv) -> None:
+              H, D, Dv, workspace=None) -> None:
         if proj.dtype != torch.float32 or gate.dtype != torch.float32 or out.dtype != torch.float32 or memory.dtype != torch.float32:
             raise KernelError("the matrix-state scan takes float32 rows and states")
         if tuple(memory.shape[1:]) != (H, Dv, D):
             raise KernelError(f"the matrix-state scan wants states [slots, {H}, {Dv}, {D}], got {tuple(memory.shape)}")
+        max_chunks, scratch = 0, None
+        if workspace is not None and self.SCAN_CHUNK and batch.max_q_len >= self.SCAN_CHUNK_MIN_ROWS:
+            # Sized by the step's rows and segments alone, so that a recorded step finds the same launches.
+            max_chunks = -(-batch.num_tokens // self.SCAN_CHUNK) + batch.num_segments
+            scratch = workspace.buffer("recurrent.chunks", (max_chunks * H * (2 * Dv * D + 2 * D + 3),), torch.float32)
+            self.launches += 2
         self._count("matrix_state_scan")
         _check(self._recurrent.kvb_matrix_state_scan(
             mode, _ptr(proj), proj.shape[1], q_col, k_col, v_col, _ptr(gate), gate.shape[1], g0, g1, float(p0), float(q_scale),
             float(floor), _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_slot), _ptr(memory), _ptr(normalizer),
-            _ptr(maximum), _ptr(out), batch.num_segments, H, D, Dv, self._stream()), "matrix_state_scan")
+            _ptr(maximum), _ptr(out), batch.num_segments, H, D, Dv, self.SCAN_CHUNK, max_chunks, _ptr(scratch), self._stream()),
+            "matrix_state_scan")
 
     def gated_linear_scan(self, proj: torch.Tensor, cols, z: torch.Tensor, tau: float, q_scale: float, batch: StepBatch,
-                          memory: torch.Tensor, out: torch.Tensor, H: int, D: int, Dv: int) -> None:
+                          memory: torch.Tensor, out: torch.Tensor, H: int, D: int, Dv: int, workspace=None) -> None:
         """Per segment, from and into memory[slot] ([H, Dv, D], float32): S = diag(a_t) S + k_t v_t^T, out_t = S^T (q_t q_scale),
         a_t = sigmoid(z_t)^(1 / tau) per key channel; q, k, v at columns `cols` of the float32 rows `proj`."""
-        self._scan(0, proj, cols[0], cols[1], cols[2], z, 0, 0, tau, q_scale, 0.0, batch, memory, None, None, out, H, D, Dv)
+        self._scan(0, proj, cols[0], cols[1], cols[2], z, 0, 0, tau, q_scale, 0.0, batch, memory, None, None, out, H, D, Dv, workspace)
 
     def matrix_memory_scan(self, proj: torch.Tensor, cols, cap: float, q_scale: float, floor: float, batch: StepBatch,
                            memory: torch.Tensor, normalizer: torch.Tensor, maximum: torch.Tensor, out: torch.Tensor, H: int, D: int,
-                           Dv: int) -> None:
+                           Dv: int, workspace=None) -> None:
         """Per segment, from and into (memory, normalizer, maximum)[slot]: i = cap tanh(x_i / cap), f = logsigmoid(cap tanh(x_f / cap)),
         m' = max(f + m, i), S = e^{f + m - m'} S + e^{i - m'} k v^T, n likewise with k, out = S^T q / (max(|n . q|, e^{-m'}) + floor);
         q, k, v and the gates' pre-activations x_i, x_f (one per head) at columns `cols` of `proj`."""
         self._scan(1, proj, cols[0], cols[1], cols[2], proj, cols[3], cols[4], cap, q_scale, floor, batch, memory, normalizer, maximum,
-                   out, H, D, Dv)
+                   out, H, D, Dv, workspace)
 
     def sample(self, logits: torch.Tensor, temperature: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor,
                out: torch.Tensor, scratch_val: torch.Tensor, scratch_idx: torch.Tensor) -> None:

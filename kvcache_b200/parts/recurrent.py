@@ -115,7 +115,7 @@ class GatedLinearAttention(_MatrixStateMixer):
         k.linear(low, self.w_a2, z, self.b_a2)
         o = ws.buffer("recurrent.o", (T, self.heads_width), torch.float32)
         k.gated_linear_scan(proj, (self.q_col, self.k_col, self.v_col), z, self.tau, self.q_scale, ctx.batch,
-                            ctx.state["memory"], o, self.num_heads, self.dim, self.vdim)
+                            ctx.state["memory"], o, self.num_heads, self.dim, self.vdim, ws)
         k.head_norm_gate(o, self.norm, self.eps, (proj, self.g_col), "silu", scale, out, out_col, self.num_heads, self.vdim)
 
 
@@ -160,7 +160,7 @@ class MatrixMemory(_MatrixStateMixer):
         o = ws.buffer("recurrent.o", (x.shape[0], self.heads_width), torch.float32)
         k.matrix_memory_scan(proj, (self.q_col, self.k_col, self.v_col, self.i_col, self.f_col), self.gate_cap, self.q_scale,
                              self.DENOMINATOR_FLOOR, ctx.batch, ctx.state["memory"], ctx.state["normalizer"], ctx.state["maximum"],
-                             o, self.num_heads, self.dim, self.vdim)
+                             o, self.num_heads, self.dim, self.vdim, ws)
         k.head_norm_gate(o, self.norm, self.eps, (proj, self.g_col), "sigmoid", scale, out, out_col, self.num_heads, self.vdim)
 
 

@@ -126,6 +126,38 @@ def test_matrix_memory_scan(kernels, H, D, Dv):
         assert_close(g, r, 5e-5, what)
 
 
+@pytest.mark.parametrize("mode", ["channel decay", "exponential gates"])
+@pytest.mark.parametrize("H,D,Dv", [(3, 24, 16), (2, 64, 128), (1, 130, 40)])
+def test_scans_in_chunks_side_by_side(kernels, mode, H, D, Dv):
+    """A step with a long segment is scanned in chunks of 64 tokens that run side by side: segments that end inside a
+    chunk, at a chunk's edge, one token after it, a single token and a segment that continues a state, against the
+    plain statement; the states left in the slots too."""
+    from kvcache_b200.engine.workspace import Workspace
+    segments, slots = [(0, 300), (40, 1), (7, 128), (0, 65), (3, 63)], [1, 4, 0, 2, 5]
+    batch = _segments_batch(segments, slots)
+    assert batch.max_q_len >= kernels.SCAN_CHUNK_MIN_ROWS
+    T = batch.num_tokens
+    cols = (0, H * D, 2 * H * D, 2 * H * D + H * Dv, 2 * H * D + H * Dv + H)
+    proj = _rand(T, cols[4] + H, seed=4)
+    proj[:, cols[3]:cols[3] + H] = proj[:, cols[3]:cols[3] + H] * 3 - 2
+    proj[:, cols[4]:cols[4] + H] = proj[:, cols[4]:cols[4] + H] * 3 + 3
+    z = _rand(T, H * D, seed=2, scale=2.0) + 3.0
+    memory, normalizer, maximum = _rand(6, H, Dv, D, seed=5), _rand(6, H, D, seed=6), _rand(6, H, seed=7).abs()
+    for t in (memory, normalizer, maximum):
+        t[1].zero_(), t[2].zero_()
+    ref = [memory.clone(), normalizer.clone(), maximum.clone(), torch.zeros(T, H * Dv)]
+    got = [memory.clone().to(DEV), normalizer.clone().to(DEV), maximum.clone().to(DEV), torch.zeros(T, H * Dv, device=DEV)]
+    if mode == "channel decay":
+        TorchKernels(wide=True).gated_linear_scan(proj, cols[:3], z, 5.0, 0.3, batch, ref[0], ref[3], H, D, Dv)
+        kernels.gated_linear_scan(proj.to(DEV), cols[:3], z.to(DEV), 5.0, 0.3, batch_to(batch, DEV), got[0], got[3], H, D, Dv, Workspace(DEV))
+    else:
+        TorchKernels(wide=True).matrix_memory_scan(proj, cols, 6.0, 0.25, 1e-6, batch, ref[0], ref[1], ref[2], ref[3], H, D, Dv)
+        kernels.matrix_memory_scan(proj.to(DEV), cols, 6.0, 0.25, 1e-6, batch_to(batch, DEV), got[0], got[1], got[2], got[3], H, D, Dv, Workspace(DEV))
+    for g, r, what in zip(got, ref, ("memory", "normalizer", "maximum", "read-out")):
+        assert_close(g, r, 5e-5, what)
+    assert torch.equal(got[0][3].cpu(), memory[3])
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,Dv,per_head,act", [(3, 16, False, "silu"), (2, 70, True, "sigmoid"), (1, 3, True, "silu"), (16, 128, False, "sigmoid")])
 def test_head_norm_gate_and_head_gate(kernels, dtype, H, Dv, per_head, act):
@@ -311,6 +343,22 @@ def test_four_ways_of_cutting(tmp_path, kernels, name, dtype):
         alone = plain.logits_of(config, weights, toks)
         assert_model_close(got[k], alone, dtype, f"mixed {k}", _spread(config, weights, toks, alone))
     kernels.check_errors()
+
+
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_long_prompts_whose_states_are_scanned_in_chunks(tmp_path, kernels, name):
+    """float32: a prompt long enough for the chunked scans, whole, in two long portions and beside another request."""
+    runner, config, weights = _runner(tmp_path, kernels, name, "float32", num_pages=160, max_tokens_per_step=700, max_tokens_per_request=700)
+    from kvcache_b200.engine.runner import StepEntry
+    tokens, other = random_tokens(config["vocab"], 600, 11), random_tokens(config["vocab"], 90, 12)
+    want = plain.logits_of(config, weights, tokens)
+    assert_close(replay_modes.whole(runner, tokens), want, 2e-4, "whole")
+    assert_close(replay_modes.portions(runner, tokens, [290, 310]), want, 2e-4, "two portions")
+    sa, sb = runner.cache.admit(), runner.cache.admit()
+    got = runner.step([StepEntry(sb, other[:60], []), StepEntry(sa, tokens[:333], list(range(333)))]).clone()
+    more = runner.step([StepEntry(sa, tokens[333:], list(range(267))), StepEntry(sb, other[60:], [29])]).clone()
+    assert_close(torch.cat([got, more[:267]]), want, 2e-4, "beside another request")
+    assert_close(more[267:], plain.logits_of(config, weights, other)[-1:], 2e-4, "the other request")
 
 
 @pytest.mark.parametrize("name", ["A", "B"])

@@ -295,7 +295,7 @@ class TorchKernels:
         for s in range(batch.num_segments):
             yield int(batch.seg_q_start[s]), int(batch.seg_q_len[s]), int(batch.seg_slot[s])
 
-    def gated_linear_scan(self, proj, cols, z, tau, q_scale, batch, memory, out, H, D, Dv):
+    def gated_linear_scan(self, proj, cols, z, tau, q_scale, batch, memory, out, H, D, Dv, workspace=None):
         f = self.f
         qc, kc, vc = cols
         for lo, n, slot in self._segments(batch):
@@ -309,7 +309,7 @@ class TorchKernels:
                 out[r] = torch.einsum("hvd,hd->hv", S, q).reshape(-1).to(out.dtype)
             memory[slot] = S.to(memory.dtype)
 
-    def matrix_memory_scan(self, proj, cols, cap, q_scale, floor, batch, memory, normalizer, maximum, out, H, D, Dv):
+    def matrix_memory_scan(self, proj, cols, cap, q_scale, floor, batch, memory, normalizer, maximum, out, H, D, Dv, workspace=None):
         f = self.f
         qc, kc, vc, ic, fc = cols
         for lo, n, slot in self._segments(batch):
