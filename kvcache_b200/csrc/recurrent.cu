@@ -10,7 +10,8 @@
 //
 // The scan keeps everything in float32.  A warp owns CPW value channels (columns of S) of one head; lane l holds the
 // key channels l, l + 32, ... of those columns in registers for the whole segment, so a token costs two fused
-// multiply-adds per held number, one shuffle tree per column, and no barrier.  A column's sum over the key channels
+// multiply-adds per held number and one shuffle tree per column; the rows of 32 tokens at a time are staged in shared
+// memory by the whole block, and the exponential gates of those tokens are computed once for the block.  A column's sum over the key channels
 // is taken in one order (lane-local over l + 32 i, then the xor tree), whatever the step holds: a token's result is
 // bit for bit the same in a prompt, a portion or alone.  State layout: [slot, head, value channel, key channel].
 //
@@ -26,7 +27,8 @@ enum { SCAN_CHANNEL_DECAY = 0, SCAN_EXP_GATES = 1 };
 
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
-// SCAN_CHANNEL_DECAY: decay per key channel d = sigmoid(z[r, h, d])^(1 / p0)  (z: `gate`, row stride gate_stride), gain 1.
+// SCAN_CHANNEL_DECAY: decay per key channel d = sigmoid(z[r, h, d])^(1 / p0), gain 1; the launcher turns the logits z
+//                     (`gate`, row stride gate_stride) into the decays in place before the scan, once for all warps.
 // SCAN_EXP_GATES:     per head i = p0 tanh(gate[r, g0 + h] / p0), f = logsigmoid(p0 tanh(gate[r, g1 + h] / p0));
 //                     m' = max(f + m, i); decay e^{f + m - m'}, gain e^{i - m'}; n' = decay n + gain k;
 //                     o = S'^T q / (max(|n' . q|, e^{-m'}) + floor).  n: [slot, head, key channel], m: [slot, head].
@@ -84,7 +86,8 @@ __global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 1024 : 256) matrix_st
     }
     pdl_wait();
     pdl_launch_dependents();
-    float S[CPW][RPL], nz[RPL], total[RPL], m = 0.f, F = 0.f;
+    __shared__ float gate_s[3][32], max_s[33], carry_s[2];     // exponential gates: see the loop
+    float S[CPW][RPL], nz[RPL], total[RPL], m = 0.f;
     float* mem = memory + ((size_t)slot * H + h) * Dv * D;
     const size_t cid = (size_t)blockIdx.z * H + h;             // (chunk id, head) in the scratch arrays
     const float* from = PASS == SCAN_FROM_START ? ch.start_S + cid * Dv * D : mem;
@@ -105,57 +108,95 @@ __global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 1024 : 256) matrix_st
             nz[i] = (PASS != SCAN_LOCAL && d < D) ? n_from[d] : 0.f;
         }
         m = PASS == SCAN_LOCAL ? -FLT_MAX : PASS == SCAN_FROM_START ? ch.start_m[cid] : maximum[(size_t)slot * H + h];
-        if (PASS == SCAN_WHOLE) __syncthreads();   // every warp has read n and m before the first may write them
+        if (threadIdx.x == 0) {
+            carry_s[0] = m;                        // the running maximum, and the sum of the log forget gates
+            carry_s[1] = 0.f;
+        }
+        // Every warp has read n and m before the first may write them (the loop's first barrier comes before any write).
     }
-    // The rows of the next token are fetched while this one is computed: none of them depends on the state.
-    float q[RPL], k[RPL], a[RPL], v[CPW], gi = 0.f, gf = 0.f;
-    auto fetch = [&](int r) {
-        const float* row = proj + (size_t)r * P;
+    // The rows of 32 tokens at a time are staged in shared memory by the whole block (one round of loads in flight
+    // instead of one per token): q and k of the head, the decays (channel-decay form), and the block's value channels.
+    extern __shared__ float tile_s[];
+    const int VC = warps * CPW, v_base = blockIdx.x * VC;
+    float* q_s = tile_s;                                       // [32][D]
+    float* k_s = q_s + 32 * D;                                 // [32][D]
+    float* a_s = k_s + 32 * D;                                 // [32][D], channel-decay form only
+    float* v_s = a_s + (MODE == SCAN_CHANNEL_DECAY ? 32 * D : 0);   // [32][VC]
+    for (int t = 0; t < n_rows; ++t) {
+        const int r = r0 + t, tt = t & 31;
+        if (tt == 0) {
+            __syncthreads();                                   // the tile before has been used up
+            const int rows = min(32, n_rows - t);
+            for (int idx = threadIdx.x; idx < rows * D; idx += blockDim.x) {
+                const int row = idx / D, d = idx - row * D;
+                const float* src = proj + (size_t)(r + row) * P;
+                q_s[idx] = src[q_col + h * D + d];
+                k_s[idx] = src[k_col + h * D + d];
+                if (MODE == SCAN_CHANNEL_DECAY) a_s[idx] = gate[(size_t)(r + row) * gate_stride + g0 + h * D + d];
+            }
+            for (int idx = threadIdx.x; idx < rows * VC; idx += blockDim.x) {
+                const int row = idx / VC, c = idx - row * VC;
+                v_s[idx] = v_base + c < Dv ? proj[(size_t)(r + row) * P + v_col + h * Dv + v_base + c] : 0.f;
+            }
+            if (MODE == SCAN_CHANNEL_DECAY) __syncthreads();
+            if (MODE == SCAN_EXP_GATES) {
+                // The gates of the tile's tokens, once for the block: thread j takes token t + j's two logarithms, the
+                // first thread walks the maximum through them, then thread j takes the token's three exponentials.
+                const int j = threadIdx.x;
+                float li = 0.f, lf = 0.f;
+                if (j < 32 && t + j < n_rows) {
+                    const float* grow = gate + (size_t)(r + j) * gate_stride;
+                    li = p0 * tanhf(grow[g0 + h] / p0);
+                    lf = log_sigmoid(p0 * tanhf(grow[g1 + h] / p0));
+                    gate_s[0][j] = lf;
+                    gate_s[1][j] = li;
+                }
+                __syncthreads();
+                if (j == 0) {
+                    float mm = carry_s[0], ff = carry_s[1];
+                    for (int u = 0; u < 32 && t + u < n_rows; ++u) {
+                        max_s[u] = mm;                               // the maximum before token t + u
+                        mm = fmaxf(gate_s[0][u] + mm, gate_s[1][u]);
+                        ff += gate_s[0][u];
+                    }
+                    max_s[32] = mm;
+                    carry_s[1] = ff;
+                }
+                __syncthreads();
+                if (j < 32 && t + j < n_rows) {
+                    const float before = max_s[j], after = fmaxf(lf + before, li);
+                    gate_s[0][j] = expf(lf + before - after);
+                    gate_s[1][j] = expf(li - after);
+                    gate_s[2][j] = expf(-after);
+                }
+                if (j == 0) carry_s[0] = max_s[32];
+                __syncthreads();
+            }
+        }
+        float qc[RPL], kc[RPL], ac[RPL], vc[CPW];
 #pragma unroll
         for (int i = 0; i < RPL; ++i) {
             const int d = lane + 32 * i;
-            q[i] = d < D ? row[q_col + h * D + d] : 0.f;
-            k[i] = d < D ? row[k_col + h * D + d] : 0.f;
-            if (MODE == SCAN_CHANNEL_DECAY) a[i] = d < D ? gate[(size_t)r * gate_stride + g0 + h * D + d] : 0.f;
+            qc[i] = d < D ? q_s[tt * D + d] * q_scale : 0.f;
+            kc[i] = d < D ? k_s[tt * D + d] : 0.f;
+            ac[i] = (MODE == SCAN_CHANNEL_DECAY && d < D) ? a_s[tt * D + d] : 0.f;
         }
 #pragma unroll
-        for (int c = 0; c < CPW; ++c) v[c] = c0 + c < Dv ? row[v_col + h * Dv + c0 + c] : 0.f;
-        if (MODE == SCAN_EXP_GATES) {
-            gi = gate[(size_t)r * gate_stride + g0 + h];
-            gf = gate[(size_t)r * gate_stride + g1 + h];
-        }
-    };
-    if (n_rows > 0) fetch(r0);
-    for (int t = 0; t < n_rows; ++t) {
-        const int r = r0 + t;
-        float qc[RPL], kc[RPL], ac[RPL], vc[CPW];
-        const float gic = gi, gfc = gf;
-#pragma unroll
-        for (int i = 0; i < RPL; ++i) { qc[i] = q[i] * q_scale; kc[i] = k[i]; ac[i] = a[i]; }
-#pragma unroll
-        for (int c = 0; c < CPW; ++c) vc[c] = v[c];
-        if (t + 1 < n_rows) fetch(r + 1);
+        for (int c = 0; c < CPW; ++c) vc[c] = v_s[tt * VC + warp * CPW + c];
         float keep = 1.f, take = 1.f, denom = 1.f;
-        if (MODE == SCAN_CHANNEL_DECAY) {
-#pragma unroll
-            for (int i = 0; i < RPL; ++i) {
-                ac[i] = expf(log_sigmoid(ac[i]) / p0);
-                if (PASS == SCAN_LOCAL) total[i] *= ac[i];
-            }
-        } else {
-            const float li = p0 * tanhf(gic / p0), lf = log_sigmoid(p0 * tanhf(gfc / p0));
-            if (PASS == SCAN_LOCAL) F += lf;
-            const float m_new = fmaxf(lf + m, li);
-            keep = expf(lf + m - m_new);
-            take = expf(li - m_new);
-            m = m_new;
+        if (MODE == SCAN_EXP_GATES) {
+            keep = gate_s[0][tt];
+            take = gate_s[1][tt];
             float part = 0.f;
 #pragma unroll
             for (int i = 0; i < RPL; ++i) {
                 nz[i] = keep * nz[i] + take * kc[i];
                 part += nz[i] * qc[i];
             }
-            if (PASS != SCAN_LOCAL) denom = fmaxf(fabsf(warp_sum(part)), expf(-m_new)) + floor_;
+            if (PASS != SCAN_LOCAL) denom = 1.f / (fmaxf(fabsf(warp_sum(part)), gate_s[2][tt]) + floor_);
+        } else if (PASS == SCAN_LOCAL) {
+#pragma unroll
+            for (int i = 0; i < RPL; ++i) total[i] *= ac[i];
         }
         if (PASS == SCAN_LOCAL) {                 // the state only
 #pragma unroll
@@ -178,7 +219,7 @@ __global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 1024 : 256) matrix_st
                 part += S[c][i] * qc[i];
             }
             o[c] = warp_sum(part);
-            if (MODE == SCAN_EXP_GATES) o[c] = o[c] / denom;
+            if (MODE == SCAN_EXP_GATES) o[c] = o[c] * denom;
         }
 #pragma unroll
         for (int c = 0; c < CPW; ++c)
@@ -210,14 +251,22 @@ __global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 1024 : 256) matrix_st
         const int d = lane + 32 * i;
         if (d < D) n_to[d] = nz[i];
     }
-    if (lane == 0) {
+    if (lane == 0) {                                           // thread 0: it wrote the carries itself
         if (PASS == SCAN_LOCAL) {
-            ch.local_m[cid] = m;
-            ch.local_F[cid] = F;
+            ch.local_m[cid] = carry_s[0];
+            ch.local_F[cid] = carry_s[1];
         } else {
-            maximum[(size_t)slot * H + h] = m;
+            maximum[(size_t)slot * H + h] = carry_s[0];
         }
     }
+}
+
+// z -> sigmoid(z)^(1 / tau) = exp(logsigmoid(z) / tau), in place.
+__global__ void channel_decay_kernel(float* __restrict__ z, size_t total, float tau) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        z[i] = expf(log_sigmoid(z[i]) / tau);
 }
 
 // Launch (2) of the chunked form: one block per (head, segment) walks the segment's chunks in order.
@@ -279,10 +328,15 @@ static void launch_scan(const float* proj, int P, int q_col, int k_col, int v_co
     // The exponential-gate form: all of a head's columns in one block.  The other: blocks of up to 8 warps.
     const int warps = MODE == SCAN_EXP_GATES ? total_warps : (total_warps < 8 ? total_warps : 8);
     const int col_blocks = (total_warps + warps - 1) / warps;
+    const size_t smem = (size_t)32 * ((MODE == SCAN_CHANNEL_DECAY ? 3 : 2) * D + warps * CPW) * sizeof(float);
 #define KVB_SCAN_PASS(PASS, Z)                                                                                                  \
-    kvb_launch(matrix_state_scan_kernel<MODE, RPL, CPW, PASS>, dim3(col_blocks, H, Z), dim3(32 * warps), 0, stream, proj, P, q_col, \
-               k_col, v_col, gate, gate_stride, g0, g1, p0, q_scale, floor_, seg_q_start, seg_q_len, seg_slot, memory, normalizer,  \
-               maximum, out, H, D, Dv, ch)
+    do {                                                                                                                        \
+        if (smem + 2048 > 48 * 1024)                                                                                            \
+            cudaFuncSetAttribute(matrix_state_scan_kernel<MODE, RPL, CPW, PASS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        kvb_launch(matrix_state_scan_kernel<MODE, RPL, CPW, PASS>, dim3(col_blocks, H, Z), dim3(32 * warps), smem, stream, proj, P,  \
+                   q_col, k_col, v_col, gate, gate_stride, g0, g1, p0, q_scale, floor_, seg_q_start, seg_q_len, seg_slot, memory,    \
+                   normalizer, maximum, out, H, D, Dv, ch);                                                                     \
+    } while (0)
     if (max_chunks <= 0) {
         KVB_SCAN_PASS(SCAN_WHOLE, S);
         return;
@@ -295,7 +349,8 @@ static void launch_scan(const float* proj, int P, int q_col, int k_col, int v_co
 }
 
 // proj: float32 [T, P] with q at q_col (H * D numbers), k at k_col, v at v_col (H * Dv).  `gate`: float32 rows of
-// stride gate_stride - per-channel decay logits at g0 (mode 0), or the two gates' pre-activations at g0 and g1 (mode 1).
+// stride gate_stride - per-channel decay logits [T, H * D] (mode 0; overwritten by the decays), or the two gates'
+// pre-activations at g0 and g1 (mode 1).
 // `max_chunks` > 0: the chunked form with chunks of `chunk_len` tokens; `max_chunks` bounds the step's chunk count
 // (sum over segments of ceil(len / chunk_len)) and `scratch` holds that many times H * (2 Dv D + 2 D + 3) floats.
 // scratch floats: max_chunks * H * (2 * Dv * D + 2 * D + 3).
@@ -303,7 +358,7 @@ static void launch_scan(const float* proj, int P, int q_col, int k_col, int v_co
 KVB_API int kvb_matrix_state_scan(int mode, const float* proj, int P, int q_col, int k_col, int v_col, const float* gate,
                                   int gate_stride, int g0, int g1, float p0, float q_scale, float floor_, const int* seg_q_start,
                                   const int* seg_q_len, const int* seg_slot, float* memory, float* normalizer, float* maximum,
-                                  float* out, int S, int H, int D, int Dv, int chunk_len, int max_chunks, float* scratch,
+                                  float* out, int T, int S, int H, int D, int Dv, int chunk_len, int max_chunks, float* scratch,
                                   cudaStream_t stream) {
     if (S <= 0) return KVB_OK;
     if (H < 1 || D < 1 || Dv < 1 || (mode != SCAN_CHANNEL_DECAY && mode != SCAN_EXP_GATES)) return KVB_ERR_SHAPE;
@@ -321,6 +376,14 @@ KVB_API int kvb_matrix_state_scan(int mode, const float* proj, int P, int q_col,
         ch.local_F = ch.start_vec + vecs;
         ch.local_m = ch.local_F + ones;
         ch.start_m = ch.local_m + ones;
+    }
+    if (mode == SCAN_CHANNEL_DECAY) {
+        if (g0 != 0 || gate_stride != H * D) return KVB_ERR_SHAPE;       // the logits are rows of their own
+        const size_t total = (size_t)T * H * D;
+        size_t blocks = (total + 255) / 256;
+        const size_t most = (size_t)kvb_sm_count() * 16;
+        if (blocks > most) blocks = most;
+        kvb_launch(channel_decay_kernel, dim3((int)blocks), dim3(256), 0, stream, const_cast<float*>(gate), total, p0);
     }
     const int rpl = D <= 32 ? 1 : D <= 64 ? 2 : D <= 128 ? 4 : 8;
     const int cpw = Dv <= 32 ? 1 : Dv <= 128 ? 4 : 8;

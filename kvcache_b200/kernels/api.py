@@ -103,7 +103,7 @@ _SIGNATURES = {
     "recurrent": {
         "kvb_matrix_state_scan": [_c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_float,
                                   _c_float, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
-                                  _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+                                  _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
         "kvb_head_norm_gate": [_c_int, _c_void_p, _c_void_p, _c_int, _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p,
                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
         "kvb_head_gate": [_c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -1042,13 +1042,15 @@ class CudaKernels(KernelSet):
         _check(self._recurrent.kvb_matrix_state_scan(
             mode, _ptr(proj), proj.shape[1], q_col, k_col, v_col, _ptr(gate), gate.shape[1], g0, g1, float(p0), float(q_scale),
             float(floor), _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_slot), _ptr(memory), _ptr(normalizer),
-            _ptr(maximum), _ptr(out), batch.num_segments, H, D, Dv, self.SCAN_CHUNK, max_chunks, _ptr(scratch), self._stream()),
-            "matrix_state_scan")
+            _ptr(maximum), _ptr(out), proj.shape[0], batch.num_segments, H, D, Dv, self.SCAN_CHUNK, max_chunks, _ptr(scratch),
+            self._stream()), "matrix_state_scan")
 
     def gated_linear_scan(self, proj: torch.Tensor, cols, z: torch.Tensor, tau: float, q_scale: float, batch: StepBatch,
                           memory: torch.Tensor, out: torch.Tensor, H: int, D: int, Dv: int, workspace=None) -> None:
         """Per segment, from and into memory[slot] ([H, Dv, D], float32): S = diag(a_t) S + k_t v_t^T, out_t = S^T (q_t q_scale),
-        a_t = sigmoid(z_t)^(1 / tau) per key channel; q, k, v at columns `cols` of the float32 rows `proj`."""
+        a_t = sigmoid(z_t)^(1 / tau) per key channel; q, k, v at columns `cols` of the float32 rows `proj`.  `z` [T, H * D] is
+        overwritten by the decays."""
+        self.launches += 1
         self._scan(0, proj, cols[0], cols[1], cols[2], z, 0, 0, tau, q_scale, 0.0, batch, memory, None, None, out, H, D, Dv, workspace)
 
     def matrix_memory_scan(self, proj: torch.Tensor, cols, cap: float, q_scale: float, floor: float, batch: StepBatch,
