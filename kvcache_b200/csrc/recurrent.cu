@@ -8,12 +8,14 @@
 //   bigram_embed        h[r] += table[(previous token * a + token * b) mod buckets], the table's last row at position 0;
 //                       then the request's previous token becomes the last one of its segment
 //
-// The scan keeps everything in float32.  A warp owns CPW value channels (columns of S) of one head; lane l holds the
-// key channels l, l + 32, ... of those columns in registers for the whole segment, so a token costs two fused
-// multiply-adds per held number and one shuffle tree per column; the rows of 32 tokens at a time are staged in shared
-// memory by the whole block, and the exponential gates of those tokens are computed once for the block.  A column's sum over the key channels
-// is taken in one order (lane-local over l + 32 i, then the xor tree), whatever the step holds: a token's result is
-// bit for bit the same in a prompt, a portion or alone.  State layout: [slot, head, value channel, key channel].
+// The scan keeps everything in float32.  A lane owns one value channel (a column of S) of one head and keeps the
+// column's key channels in registers for the whole segment (R of them; heads with more than 128 key channels split a
+// column over KS = 2 neighbouring lanes), so a token costs a lane three multiply-adds per key channel - decay and add,
+// read-out - and no exchange between lanes but the one that joins the parts of a split column.  The rows of 32 tokens at a
+// time (q, k, the decays, the block's value channels) are staged in shared memory by the whole block and read from
+// there as broadcasts; the exponential gates of those tokens are computed once for the block.  A column's sum over the
+// key channels runs in one order whatever the step holds: a token's result is bit for bit the same in a prompt, a
+// portion or alone.  State layout: [slot, head, key channel, value channel] (a warp's loads of a key channel's row coalesce).
 //
 // Long segments are cut into chunks of L tokens that run side by side, in three launches: (1) every chunk but a
 // segment's last is scanned from an empty state and leaves its end state and its total decay in scratch; (2) per
@@ -27,33 +29,25 @@ enum { SCAN_CHANNEL_DECAY = 0, SCAN_EXP_GATES = 1 };
 
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
-// SCAN_CHANNEL_DECAY: decay per key channel d = sigmoid(z[r, h, d])^(1 / p0), gain 1; the launcher turns the logits z
-//                     (`gate`, row stride gate_stride) into the decays in place before the scan, once for all warps.
-// SCAN_EXP_GATES:     per head i = p0 tanh(gate[r, g0 + h] / p0), f = logsigmoid(p0 tanh(gate[r, g1 + h] / p0));
-//                     m' = max(f + m, i); decay e^{f + m - m'}, gain e^{i - m'}; n' = decay n + gain k;
-//                     o = S'^T q / (max(|n' . q|, e^{-m'}) + floor).  n: [slot, head, key channel], m: [slot, head].
-// grid (column blocks, heads, segments); the exponential-gate form takes one block per head (its n and m are read by
-// every warp at the start and written by the first at the end, with a barrier in between).
 // Scratch of the chunked form; chunk ids count the chunks of all segments in the order of the segments.
 struct ScanChunks {
     int L, S;              // tokens in a chunk; segments in the step
-    float* local_S;        // [chunk, H, Dv, D]   end state of the chunk scanned from an empty state
+    float* local_S;        // [chunk, H, D, Dv]   end state of the chunk scanned from an empty state
     float* local_vec;      // [chunk, H, D]       channel decay: the product of the chunk's decays; exponential gates: its normaliser
     float* local_F;        // [chunk, H]          exponential gates: the sum of the chunk's log forget gates
     float* local_m;        // [chunk, H]          exponential gates: the chunk's maximum from an empty state
-    float* start_S;        // [chunk, H, Dv, D]   state before the chunk's first token
+    float* start_S;        // [chunk, H, D, Dv]   state before the chunk's first token
     float* start_vec;      // [chunk, H, D]       exponential gates: the normaliser there
     float* start_m;        // [chunk, H]          exponential gates: the maximum there
 };
 
 // Which (segment, chunk of it) the chunk id is; false beyond the step's last chunk.
-__device__ __forceinline__ bool find_chunk(int id, const ScanChunks& ch, const int* seg_q_len, int& seg, int& index, int& count,
-                                           int& first_id) {
+__device__ __forceinline__ bool find_chunk(int id, const ScanChunks& ch, const int* seg_q_len, int& seg, int& index, int& count) {
     int at = 0;
     for (int s = 0; s < ch.S; ++s) {
         const int nc = (seg_q_len[s] + ch.L - 1) / ch.L;
         if (id < at + nc) {
-            seg = s; index = id - at; count = nc; first_id = at;
+            seg = s; index = id - at; count = nc;
             return true;
         }
         at += nc;
@@ -61,90 +55,99 @@ __device__ __forceinline__ bool find_chunk(int id, const ScanChunks& ch, const i
     return false;
 }
 
-enum { SCAN_WHOLE = 0, SCAN_LOCAL = 1, SCAN_FROM_START = 3 };
+enum { SCAN_LOCAL = 1, SCAN_FROM_START = 3 };
+constexpr int SCAN_TILE = 32;          // tokens staged at a time
 
-// PASS: SCAN_WHOLE - grid z counts segments, from and into the slots.  SCAN_LOCAL / SCAN_FROM_START - grid z counts
-// chunks (launches (1) and (3) of the chunked form).
-template <int MODE, int RPL, int CPW, int PASS>
-__global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 1024 : 256) matrix_state_scan_kernel(
+// SCAN_CHANNEL_DECAY: decay per key channel d = sigmoid(z[r, h, d])^(1 / p0), gain 1; the launcher turns the logits z
+//                     (`gate`, row stride gate_stride) into the decays in place before the scan, once for all warps.
+// SCAN_EXP_GATES:     per head i = p0 tanh(gate[r, g0 + h] / p0), f = logsigmoid(p0 tanh(gate[r, g1 + h] / p0));
+//                     m' = max(f + m, i); decay e^{f + m - m'}, gain e^{i - m'}; n' = decay n + gain k;
+//                     o = S'^T q / (max(|n' . q|, e^{-m'}) + floor).  n: [slot, head, key channel], m: [slot, head].
+// PASS: SCAN_LOCAL / SCAN_FROM_START - launches (1) and (3) of the chunked form; grid z counts chunks.  Segments in one
+// piece are SCAN_FROM_START with chunks longer than any segment and no start states (`ch.start_S` null): from the slots.
+// grid (column blocks, heads, segments or chunks); a warp holds 32 / KS columns.  The exponential-gate form takes one
+// block per head: its n and m are kept by every warp (lane l: key channels l, l + 32, ...; the same arithmetic, the same
+// bits), read at the start and written by the first warp at the end, with the loop's barriers in between.
+template <int MODE, int R, int KS, int PASS>
+__global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 512 : 128) matrix_state_scan_kernel(
     const float* __restrict__ proj, int P, int q_col, int k_col, int v_col, const float* __restrict__ gate, int gate_stride,
     int g0, int g1, float p0, float q_scale, float floor_, const int* __restrict__ seg_q_start,
     const int* __restrict__ seg_q_len, const int* __restrict__ seg_slot, float* __restrict__ memory,
     float* __restrict__ normalizer, float* __restrict__ maximum, float* __restrict__ out, int H, int D, int Dv, ScanChunks ch) {
+    constexpr int RK = R * KS;                                 // key channels of a staged row, zero beyond D
+    constexpr int NPL = RK / 32;                               // normaliser entries a lane keeps
+    constexpr int COLS = 32 / KS;                              // columns of a warp
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const int h = blockIdx.y;
-    const int c0 = (blockIdx.x * warps + warp) * CPW;
-    int seg = blockIdx.z, chunk = 0, chunks = 1, first_id = 0;
-    if (PASS != SCAN_WHOLE && !find_chunk(blockIdx.z, ch, seg_q_len, seg, chunk, chunks, first_id)) return;
+    const int part = lane % KS;                                // which run of R key channels of its column the lane holds
+    const int VC = warps * COLS;                               // columns of the block
+    const int col = blockIdx.x * VC + warp * COLS + lane / KS;
+    const bool col_ok = col < Dv;
+    int seg = blockIdx.z, chunk = 0, chunks = 1;
+    if (!find_chunk(blockIdx.z, ch, seg_q_len, seg, chunk, chunks)) return;
     const bool last_chunk = chunk == chunks - 1;
     if (PASS == SCAN_LOCAL && last_chunk) return;              // nobody starts from its end
     int r0 = seg_q_start[seg], n_rows = seg_q_len[seg];
     const int slot = seg_slot[seg];
-    if (PASS != SCAN_WHOLE) {
-        r0 += chunk * ch.L;
-        n_rows = min(ch.L, n_rows - chunk * ch.L);
-    }
+    r0 += chunk * ch.L;
+    n_rows = min(ch.L, n_rows - chunk * ch.L);
     pdl_wait();
     pdl_launch_dependents();
-    __shared__ float gate_s[3][32], max_s[33], carry_s[2];     // exponential gates: see the loop
-    float S[CPW][RPL], nz[RPL], total[RPL], m = 0.f;
-    float* mem = memory + ((size_t)slot * H + h) * Dv * D;
+    __shared__ float gate_s[3][SCAN_TILE], max_s[SCAN_TILE + 1], carry_s[2];     // exponential gates: see the loop
+    extern __shared__ __align__(16) float tile_s[];
+    float* q_s = tile_s;                                       // [tile][RK], already times q_scale
+    float* k_s = q_s + SCAN_TILE * RK;                         // [tile][RK]
+    float* a_s = k_s + SCAN_TILE * RK;                         // [tile][RK], channel-decay form only
+    float* v_s = a_s + (MODE == SCAN_CHANNEL_DECAY ? SCAN_TILE * RK : 0);   // [tile][VC]
+    float S[R], nz[NPL], total[NPL];
+    float* mem = memory + ((size_t)slot * H + h) * D * Dv;
     const size_t cid = (size_t)blockIdx.z * H + h;             // (chunk id, head) in the scratch arrays
-    const float* from = PASS == SCAN_FROM_START ? ch.start_S + cid * Dv * D : mem;
+    const bool from_slot = ch.start_S == nullptr;
+    const float* from = from_slot ? mem : ch.start_S + cid * D * Dv;
 #pragma unroll
-    for (int c = 0; c < CPW; ++c)
+    for (int i = 0; i < R; ++i) {
+        const int d = part * R + i;
+        S[i] = (PASS != SCAN_LOCAL && col_ok && d < D) ? from[(size_t)d * Dv + col] : 0.f;
+    }
 #pragma unroll
-        for (int i = 0; i < RPL; ++i) {
-            const int d = lane + 32 * i;
-            S[c][i] = (PASS != SCAN_LOCAL && c0 + c < Dv && d < D) ? from[(size_t)(c0 + c) * D + d] : 0.f;
-        }
-#pragma unroll
-    for (int i = 0; i < RPL; ++i) total[i] = 1.f;
+    for (int i = 0; i < NPL; ++i) total[i] = 1.f;
     if (MODE == SCAN_EXP_GATES) {
-        const float* n_from = PASS == SCAN_FROM_START ? ch.start_vec + cid * D : normalizer + ((size_t)slot * H + h) * D;
+        const float* n_from = from_slot ? normalizer + ((size_t)slot * H + h) * D : ch.start_vec + cid * D;
 #pragma unroll
-        for (int i = 0; i < RPL; ++i) {
+        for (int i = 0; i < NPL; ++i) {
             const int d = lane + 32 * i;
             nz[i] = (PASS != SCAN_LOCAL && d < D) ? n_from[d] : 0.f;
         }
-        m = PASS == SCAN_LOCAL ? -FLT_MAX : PASS == SCAN_FROM_START ? ch.start_m[cid] : maximum[(size_t)slot * H + h];
         if (threadIdx.x == 0) {
-            carry_s[0] = m;                        // the running maximum, and the sum of the log forget gates
+            // The running maximum, and the sum of the log forget gates.
+            carry_s[0] = PASS == SCAN_LOCAL ? -FLT_MAX : from_slot ? maximum[(size_t)slot * H + h] : ch.start_m[cid];
             carry_s[1] = 0.f;
         }
-        // Every warp has read n and m before the first may write them (the loop's first barrier comes before any write).
+        // Every warp has read n and m before the first may write them: the loop's first barrier comes before any write.
     }
-    // The rows of 32 tokens at a time are staged in shared memory by the whole block (one round of loads in flight
-    // instead of one per token): q and k of the head, the decays (channel-decay form), and the block's value channels.
-    extern __shared__ float tile_s[];
-    const int VC = warps * CPW, v_base = blockIdx.x * VC;
-    float* q_s = tile_s;                                       // [32][D]
-    float* k_s = q_s + 32 * D;                                 // [32][D]
-    float* a_s = k_s + 32 * D;                                 // [32][D], channel-decay form only
-    float* v_s = a_s + (MODE == SCAN_CHANNEL_DECAY ? 32 * D : 0);   // [32][VC]
+#pragma unroll 1
     for (int t = 0; t < n_rows; ++t) {
-        const int r = r0 + t, tt = t & 31;
+        const int r = r0 + t, tt = t % SCAN_TILE;
         if (tt == 0) {
             __syncthreads();                                   // the tile before has been used up
-            const int rows = min(32, n_rows - t);
-            for (int idx = threadIdx.x; idx < rows * D; idx += blockDim.x) {
-                const int row = idx / D, d = idx - row * D;
+            const int rows = min(SCAN_TILE, n_rows - t);
+            for (int idx = threadIdx.x; idx < rows * RK; idx += blockDim.x) {
+                const int row = idx / RK, d = idx - row * RK;
                 const float* src = proj + (size_t)(r + row) * P;
-                q_s[idx] = src[q_col + h * D + d];
-                k_s[idx] = src[k_col + h * D + d];
-                if (MODE == SCAN_CHANNEL_DECAY) a_s[idx] = gate[(size_t)(r + row) * gate_stride + g0 + h * D + d];
+                q_s[idx] = d < D ? src[q_col + h * D + d] * q_scale : 0.f;
+                k_s[idx] = d < D ? src[k_col + h * D + d] : 0.f;
+                if (MODE == SCAN_CHANNEL_DECAY) a_s[idx] = d < D ? gate[(size_t)(r + row) * gate_stride + g0 + h * D + d] : 0.f;
             }
             for (int idx = threadIdx.x; idx < rows * VC; idx += blockDim.x) {
                 const int row = idx / VC, c = idx - row * VC;
-                v_s[idx] = v_base + c < Dv ? proj[(size_t)(r + row) * P + v_col + h * Dv + v_base + c] : 0.f;
+                v_s[idx] = blockIdx.x * VC + c < Dv ? proj[(size_t)(r + row) * P + v_col + h * Dv + blockIdx.x * VC + c] : 0.f;
             }
-            if (MODE == SCAN_CHANNEL_DECAY) __syncthreads();
             if (MODE == SCAN_EXP_GATES) {
                 // The gates of the tile's tokens, once for the block: thread j takes token t + j's two logarithms, the
                 // first thread walks the maximum through them, then thread j takes the token's three exponentials.
                 const int j = threadIdx.x;
                 float li = 0.f, lf = 0.f;
-                if (j < 32 && t + j < n_rows) {
+                if (j < SCAN_TILE && t + j < n_rows) {
                     const float* grow = gate + (size_t)(r + j) * gate_stride;
                     li = p0 * tanhf(grow[g0 + h] / p0);
                     lf = log_sigmoid(p0 * tanhf(grow[g1 + h] / p0));
@@ -154,92 +157,82 @@ __global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 1024 : 256) matrix_st
                 __syncthreads();
                 if (j == 0) {
                     float mm = carry_s[0], ff = carry_s[1];
-                    for (int u = 0; u < 32 && t + u < n_rows; ++u) {
+                    for (int u = 0; u < SCAN_TILE && t + u < n_rows; ++u) {
                         max_s[u] = mm;                               // the maximum before token t + u
                         mm = fmaxf(gate_s[0][u] + mm, gate_s[1][u]);
                         ff += gate_s[0][u];
                     }
-                    max_s[32] = mm;
+                    max_s[SCAN_TILE] = mm;
                     carry_s[1] = ff;
                 }
                 __syncthreads();
-                if (j < 32 && t + j < n_rows) {
+                if (j < SCAN_TILE && t + j < n_rows) {
                     const float before = max_s[j], after = fmaxf(lf + before, li);
                     gate_s[0][j] = expf(lf + before - after);
                     gate_s[1][j] = expf(li - after);
                     gate_s[2][j] = expf(-after);
                 }
-                if (j == 0) carry_s[0] = max_s[32];
-                __syncthreads();
+                if (j == 0) carry_s[0] = max_s[SCAN_TILE];
             }
+            __syncthreads();
         }
-        float qc[RPL], kc[RPL], ac[RPL], vc[CPW];
-#pragma unroll
-        for (int i = 0; i < RPL; ++i) {
-            const int d = lane + 32 * i;
-            qc[i] = d < D ? q_s[tt * D + d] * q_scale : 0.f;
-            kc[i] = d < D ? k_s[tt * D + d] : 0.f;
-            ac[i] = (MODE == SCAN_CHANNEL_DECAY && d < D) ? a_s[tt * D + d] : 0.f;
-        }
-#pragma unroll
-        for (int c = 0; c < CPW; ++c) vc[c] = v_s[tt * VC + warp * CPW + c];
-        float keep = 1.f, take = 1.f, denom = 1.f;
+        const float4* q4 = reinterpret_cast<const float4*>(q_s + tt * RK + part * R);
+        const float4* k4 = reinterpret_cast<const float4*>(k_s + tt * RK + part * R);
+        const float4* a4 = reinterpret_cast<const float4*>(a_s + tt * RK + part * R);
+        const float v = v_s[tt * VC + warp * COLS + lane / KS];
+        float keep = 1.f, gain = v, denom = 1.f;
         if (MODE == SCAN_EXP_GATES) {
             keep = gate_s[0][tt];
-            take = gate_s[1][tt];
-            float part = 0.f;
+            const float take = gate_s[1][tt];
+            gain = take * v;
+            float dot = 0.f;
 #pragma unroll
-            for (int i = 0; i < RPL; ++i) {
-                nz[i] = keep * nz[i] + take * kc[i];
-                part += nz[i] * qc[i];
+            for (int i = 0; i < NPL; ++i) {
+                const int d = lane + 32 * i;
+                nz[i] = keep * nz[i] + take * k_s[tt * RK + d];
+                dot += nz[i] * q_s[tt * RK + d];
             }
-            if (PASS != SCAN_LOCAL) denom = 1.f / (fmaxf(fabsf(warp_sum(part)), gate_s[2][tt]) + floor_);
-        } else if (PASS == SCAN_LOCAL) {
+            if (PASS != SCAN_LOCAL) denom = 1.f / (fmaxf(fabsf(warp_sum(dot)), gate_s[2][tt]) + floor_);
+        } else if (PASS == SCAN_LOCAL && blockIdx.x == 0 && warp == 0) {
 #pragma unroll
-            for (int i = 0; i < RPL; ++i) total[i] *= ac[i];
+            for (int i = 0; i < NPL; ++i) total[i] *= (lane + 32 * i < D) ? a_s[tt * RK + lane + 32 * i] : 1.f;
         }
-        if (PASS == SCAN_LOCAL) {                 // the state only
+        float o = 0.f;
 #pragma unroll
-            for (int c = 0; c < CPW; ++c)
-#pragma unroll
-                for (int i = 0; i < RPL; ++i) {
-                    if (MODE == SCAN_CHANNEL_DECAY) S[c][i] = ac[i] * S[c][i] + kc[i] * vc[c];
-                    else S[c][i] = keep * S[c][i] + take * (kc[i] * vc[c]);
-                }
-            continue;
-        }
-        float o[CPW];
-#pragma unroll
-        for (int c = 0; c < CPW; ++c) {
-            float part = 0.f;
-#pragma unroll
-            for (int i = 0; i < RPL; ++i) {
-                if (MODE == SCAN_CHANNEL_DECAY) S[c][i] = ac[i] * S[c][i] + kc[i] * vc[c];
-                else S[c][i] = keep * S[c][i] + take * (kc[i] * vc[c]);
-                part += S[c][i] * qc[i];
+        for (int i = 0; i < R; i += 4) {
+            const float4 kk = k4[i >> 2];
+            float4 qq = make_float4(0.f, 0.f, 0.f, 0.f), aa = make_float4(keep, keep, keep, keep);
+            if (PASS != SCAN_LOCAL) qq = q4[i >> 2];
+            if (MODE == SCAN_CHANNEL_DECAY) aa = a4[i >> 2];
+            S[i] = fmaf(aa.x, S[i], kk.x * gain);
+            S[i + 1] = fmaf(aa.y, S[i + 1], kk.y * gain);
+            S[i + 2] = fmaf(aa.z, S[i + 2], kk.z * gain);
+            S[i + 3] = fmaf(aa.w, S[i + 3], kk.w * gain);
+            if (PASS != SCAN_LOCAL) {
+                o = fmaf(S[i], qq.x, o);
+                o = fmaf(S[i + 1], qq.y, o);
+                o = fmaf(S[i + 2], qq.z, o);
+                o = fmaf(S[i + 3], qq.w, o);
             }
-            o[c] = warp_sum(part);
-            if (MODE == SCAN_EXP_GATES) o[c] = o[c] * denom;
         }
-#pragma unroll
-        for (int c = 0; c < CPW; ++c)
-            if (lane == c && c0 + c < Dv) out[(size_t)r * H * Dv + h * Dv + c0 + c] = o[c];
+        if (PASS == SCAN_LOCAL) continue;                      // the state only
+        if (KS == 2) o += __shfl_xor_sync(0xffffffffu, o, 1);
+        if (MODE == SCAN_EXP_GATES) o *= denom;
+        if (part == 0 && col_ok) out[(size_t)r * H * Dv + h * Dv + col] = o;
     }
     if (n_rows <= 0) return;
     if (PASS == SCAN_FROM_START && !last_chunk) return;        // only a segment's last chunk leaves the state in the slot
-    float* to = PASS == SCAN_LOCAL ? ch.local_S + cid * Dv * D : mem;
+    float* to = PASS == SCAN_LOCAL ? ch.local_S + cid * D * Dv : mem;
 #pragma unroll
-    for (int c = 0; c < CPW; ++c)
-#pragma unroll
-        for (int i = 0; i < RPL; ++i) {
-            const int d = lane + 32 * i;
-            if (c0 + c < Dv && d < D) to[(size_t)(c0 + c) * D + d] = S[c][i];
-        }
+    for (int i = 0; i < R; ++i) {
+        const int d = part * R + i;
+        if (col_ok && d < D) to[(size_t)d * Dv + col] = S[i];
+    }
     if (blockIdx.x != 0 || warp != 0) return;
     if (MODE == SCAN_CHANNEL_DECAY) {
         if (PASS == SCAN_LOCAL)
 #pragma unroll
-            for (int i = 0; i < RPL; ++i) {
+            for (int i = 0; i < NPL; ++i) {
                 const int d = lane + 32 * i;
                 if (d < D) ch.local_vec[cid * D + d] = total[i];
             }
@@ -247,7 +240,7 @@ __global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 1024 : 256) matrix_st
     }
     float* n_to = PASS == SCAN_LOCAL ? ch.local_vec + cid * D : normalizer + ((size_t)slot * H + h) * D;
 #pragma unroll
-    for (int i = 0; i < RPL; ++i) {
+    for (int i = 0; i < NPL; ++i) {
         const int d = lane + 32 * i;
         if (d < D) n_to[d] = nz[i];
     }
@@ -269,23 +262,23 @@ __global__ void channel_decay_kernel(float* __restrict__ z, size_t total, float 
         z[i] = expf(log_sigmoid(z[i]) / tau);
 }
 
-// Launch (2) of the chunked form: one block per (head, segment) walks the segment's chunks in order.
+// Launch (2) of the chunked form: a thread per element of a (segment, head)'s state walks the segment's chunks in order.
 template <int MODE>
 __global__ void scan_chunk_starts_kernel(const int* __restrict__ seg_q_len, const int* __restrict__ seg_slot,
                                          const float* __restrict__ memory, const float* __restrict__ normalizer,
                                          const float* __restrict__ maximum, int H, int D, int Dv, ScanChunks ch) {
     pdl_wait();
     pdl_launch_dependents();
-    const int h = blockIdx.x, seg = blockIdx.y;
+    const int h = blockIdx.y, seg = blockIdx.z;
     int first = 0;
     for (int s = 0; s < seg; ++s) first += (seg_q_len[s] + ch.L - 1) / ch.L;
     const int chunks = (seg_q_len[seg] + ch.L - 1) / ch.L;
     if (chunks <= 0) return;
     const int slot = seg_slot[seg];
-    const size_t per = (size_t)Dv * D;
+    const size_t per = (size_t)D * Dv;
     const float* mem = memory + ((size_t)slot * H + h) * per;
-    for (size_t e = threadIdx.x; e < per; e += blockDim.x) {
-        const int d = (int)(e % D);
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < per; e += (size_t)gridDim.x * blockDim.x) {
+        const int d = (int)(e / Dv);
         float s = mem[e];
         float m = MODE == SCAN_EXP_GATES ? maximum[(size_t)slot * H + h] : 0.f;
         for (int c = 0; c < chunks; ++c) {
@@ -302,7 +295,7 @@ __global__ void scan_chunk_starts_kernel(const int* __restrict__ seg_q_len, cons
             }
         }
     }
-    if (MODE == SCAN_EXP_GATES)
+    if (MODE == SCAN_EXP_GATES && blockIdx.x == 0)
         for (int d = threadIdx.x; d < D; d += blockDim.x) {
             float n = normalizer[((size_t)slot * H + h) * D + d];
             float m = maximum[(size_t)slot * H + h];
@@ -319,30 +312,35 @@ __global__ void scan_chunk_starts_kernel(const int* __restrict__ seg_q_len, cons
         }
 }
 
-template <int MODE, int RPL, int CPW>
+template <int MODE, int R, int KS>
 static void launch_scan(const float* proj, int P, int q_col, int k_col, int v_col, const float* gate, int gate_stride, int g0, int g1,
                         float p0, float q_scale, float floor_, const int* seg_q_start, const int* seg_q_len, const int* seg_slot,
                         float* memory, float* normalizer, float* maximum, float* out, int S, int H, int D, int Dv, ScanChunks ch,
                         int max_chunks, cudaStream_t stream) {
-    const int total_warps = (Dv + CPW - 1) / CPW;
-    // The exponential-gate form: all of a head's columns in one block.  The other: blocks of up to 8 warps.
-    const int warps = MODE == SCAN_EXP_GATES ? total_warps : (total_warps < 8 ? total_warps : 8);
+    constexpr int COLS = 32 / KS;
+    const int total_warps = (Dv + COLS - 1) / COLS;
+    // The exponential-gate form: all of a head's columns in one block.  The other: blocks of up to 4 warps.
+    const int warps = MODE == SCAN_EXP_GATES ? total_warps : (total_warps < 4 ? total_warps : 4);
     const int col_blocks = (total_warps + warps - 1) / warps;
-    const size_t smem = (size_t)32 * ((MODE == SCAN_CHANNEL_DECAY ? 3 : 2) * D + warps * CPW) * sizeof(float);
+    const size_t smem = (size_t)SCAN_TILE * ((MODE == SCAN_CHANNEL_DECAY ? 3 : 2) * R * KS + warps * COLS) * sizeof(float);
 #define KVB_SCAN_PASS(PASS, Z)                                                                                                  \
     do {                                                                                                                        \
         if (smem + 2048 > 48 * 1024)                                                                                            \
-            cudaFuncSetAttribute(matrix_state_scan_kernel<MODE, RPL, CPW, PASS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        kvb_launch(matrix_state_scan_kernel<MODE, RPL, CPW, PASS>, dim3(col_blocks, H, Z), dim3(32 * warps), smem, stream, proj, P,  \
+            cudaFuncSetAttribute(matrix_state_scan_kernel<MODE, R, KS, PASS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        kvb_launch(matrix_state_scan_kernel<MODE, R, KS, PASS>, dim3(col_blocks, H, Z), dim3(32 * warps), smem, stream, proj, P,    \
                    q_col, k_col, v_col, gate, gate_stride, g0, g1, p0, q_scale, floor_, seg_q_start, seg_q_len, seg_slot, memory,    \
                    normalizer, maximum, out, H, D, Dv, ch);                                                                     \
     } while (0)
     if (max_chunks <= 0) {
-        KVB_SCAN_PASS(SCAN_WHOLE, S);
+        ScanChunks whole = {};
+        whole.L = 1 << 30;
+        whole.S = S;
+        ch = whole;
+        KVB_SCAN_PASS(SCAN_FROM_START, S);
         return;
     }
     KVB_SCAN_PASS(SCAN_LOCAL, max_chunks);
-    kvb_launch(scan_chunk_starts_kernel<MODE>, dim3(H, S), dim3(256), 0, stream, seg_q_len, seg_slot, (const float*)memory,
+    kvb_launch(scan_chunk_starts_kernel<MODE>, dim3((D * Dv + 255) / 256, H, S), dim3(256), 0, stream, seg_q_len, seg_slot, (const float*)memory,
                (const float*)normalizer, (const float*)maximum, H, D, Dv, ch);
     KVB_SCAN_PASS(SCAN_FROM_START, max_chunks);
 #undef KVB_SCAN_PASS
@@ -350,11 +348,9 @@ static void launch_scan(const float* proj, int P, int q_col, int k_col, int v_co
 
 // proj: float32 [T, P] with q at q_col (H * D numbers), k at k_col, v at v_col (H * Dv).  `gate`: float32 rows of
 // stride gate_stride - per-channel decay logits [T, H * D] (mode 0; overwritten by the decays), or the two gates'
-// pre-activations at g0 and g1 (mode 1).
+// pre-activations at g0 and g1 (mode 1).  States: memory [slots, H, D, Dv], normalizer [slots, H, D], maximum [slots, H].
 // `max_chunks` > 0: the chunked form with chunks of `chunk_len` tokens; `max_chunks` bounds the step's chunk count
 // (sum over segments of ceil(len / chunk_len)) and `scratch` holds that many times H * (2 Dv D + 2 D + 3) floats.
-// scratch floats: max_chunks * H * (2 * Dv * D + 2 * D + 3).
-
 KVB_API int kvb_matrix_state_scan(int mode, const float* proj, int P, int q_col, int k_col, int v_col, const float* gate,
                                   int gate_stride, int g0, int g1, float p0, float q_scale, float floor_, const int* seg_q_start,
                                   const int* seg_q_len, const int* seg_slot, float* memory, float* normalizer, float* maximum,
@@ -362,7 +358,8 @@ KVB_API int kvb_matrix_state_scan(int mode, const float* proj, int P, int q_col,
                                   cudaStream_t stream) {
     if (S <= 0) return KVB_OK;
     if (H < 1 || D < 1 || Dv < 1 || (mode != SCAN_CHANNEL_DECAY && mode != SCAN_EXP_GATES)) return KVB_ERR_SHAPE;
-    if (D > 256 || Dv > 256 || H > 65535 || S > 65535 || max_chunks > 65535) return KVB_ERR_LIMIT;
+    // A block of the exponential-gate form holds all of a head's columns: at most 16 warps.
+    if (D > 256 || H > 65535 || S > 65535 || max_chunks > 65535 || Dv > (D > 128 ? 256 : 512)) return KVB_ERR_LIMIT;
     if (max_chunks > 0 && (chunk_len < 1 || scratch == nullptr)) return KVB_ERR_SHAPE;
     ScanChunks ch = {};
     if (max_chunks > 0) {
@@ -385,23 +382,16 @@ KVB_API int kvb_matrix_state_scan(int mode, const float* proj, int P, int q_col,
         if (blocks > most) blocks = most;
         kvb_launch(channel_decay_kernel, dim3((int)blocks), dim3(256), 0, stream, const_cast<float*>(gate), total, p0);
     }
-    const int rpl = D <= 32 ? 1 : D <= 64 ? 2 : D <= 128 ? 4 : 8;
-    const int cpw = Dv <= 32 ? 1 : Dv <= 128 ? 4 : 8;
-#define KVB_SCAN(MODE, RPL, CPW)                                                                                              \
-    launch_scan<MODE, RPL, CPW>(proj, P, q_col, k_col, v_col, gate, gate_stride, g0, g1, p0, q_scale, floor_, seg_q_start,     \
-                                seg_q_len, seg_slot, memory, normalizer, maximum, out, S, H, D, Dv, ch, max_chunks, stream)
-#define KVB_SCAN_CPW(MODE, RPL)                                                                                               \
+#define KVB_SCAN(MODE, R, KS)                                                                                                  \
+    launch_scan<MODE, R, KS>(proj, P, q_col, k_col, v_col, gate, gate_stride, g0, g1, p0, q_scale, floor_, seg_q_start,        \
+                             seg_q_len, seg_slot, memory, normalizer, maximum, out, S, H, D, Dv, ch, max_chunks, stream)
+#define KVB_SCAN_SIZE(MODE)                                                                                                    \
     do {                                                                                                                      \
-        if (cpw == 1) KVB_SCAN(MODE, RPL, 1); else if (cpw == 4) KVB_SCAN(MODE, RPL, 4); else KVB_SCAN(MODE, RPL, 8);         \
+        if (D <= 32) KVB_SCAN(MODE, 32, 1); else if (D <= 64) KVB_SCAN(MODE, 64, 1);                                          \
+        else if (D <= 128) KVB_SCAN(MODE, 128, 1); else KVB_SCAN(MODE, 128, 2);                                               \
     } while (0)
-#define KVB_SCAN_RPL(MODE)                                                                                                    \
-    do {                                                                                                                      \
-        if (rpl == 1) KVB_SCAN_CPW(MODE, 1); else if (rpl == 2) KVB_SCAN_CPW(MODE, 2);                                        \
-        else if (rpl == 4) KVB_SCAN_CPW(MODE, 4); else KVB_SCAN_CPW(MODE, 8);                                                 \
-    } while (0)
-    if (mode == SCAN_CHANNEL_DECAY) KVB_SCAN_RPL(SCAN_CHANNEL_DECAY); else KVB_SCAN_RPL(SCAN_EXP_GATES);
-#undef KVB_SCAN_RPL
-#undef KVB_SCAN_CPW
+    if (mode == SCAN_CHANNEL_DECAY) KVB_SCAN_SIZE(SCAN_CHANNEL_DECAY); else KVB_SCAN_SIZE(SCAN_EXP_GATES);
+#undef KVB_SCAN_SIZE
 #undef KVB_SCAN
     return kvb_launch_status();
 }

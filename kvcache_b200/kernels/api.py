@@ -1030,8 +1030,8 @@ class CudaKernels(KernelSet):
               H, D, Dv, workspace=None) -> None:
         if proj.dtype != torch.float32 or gate.dtype != torch.float32 or out.dtype != torch.float32 or memory.dtype != torch.float32:
             raise KernelError("the matrix-state scan takes float32 rows and states")
-        if tuple(memory.shape[1:]) != (H, Dv, D):
-            raise KernelError(f"the matrix-state scan wants states [slots, {H}, {Dv}, {D}], got {tuple(memory.shape)}")
+        if tuple(memory.shape[1:]) != (H, D, Dv):
+            raise KernelError(f"the matrix-state scan wants states [slots, {H}, {D}, {Dv}], got {tuple(memory.shape)}")
         max_chunks, scratch = 0, None
         if workspace is not None and self.SCAN_CHUNK and batch.max_q_len >= self.SCAN_CHUNK_MIN_ROWS:
             # Sized by the step's rows and segments alone, so that a recorded step finds the same launches.
@@ -1047,7 +1047,7 @@ class CudaKernels(KernelSet):
 
     def gated_linear_scan(self, proj: torch.Tensor, cols, z: torch.Tensor, tau: float, q_scale: float, batch: StepBatch,
                           memory: torch.Tensor, out: torch.Tensor, H: int, D: int, Dv: int, workspace=None) -> None:
-        """Per segment, from and into memory[slot] ([H, Dv, D], float32): S = diag(a_t) S + k_t v_t^T, out_t = S^T (q_t q_scale),
+        """Per segment, from and into memory[slot] ([H, D, Dv], float32): S = diag(a_t) S + k_t v_t^T, out_t = S^T (q_t q_scale),
         a_t = sigmoid(z_t)^(1 / tau) per key channel; q, k, v at columns `cols` of the float32 rows `proj`.  `z` [T, H * D] is
         overwritten by the decays."""
         self.launches += 1

@@ -102,8 +102,8 @@ class GatedLinearAttention(_MatrixStateMixer):
         return super().weight_bytes() + sum(m.numel() * m.element_size() for m in (self.w_a1, self.w_a2))
 
     def state_spec(self):
-        # [head, value channel, key channel]: a value channel's column of S is contiguous.
-        return {"memory": StateSpec((self.num_heads, self.vdim, self.dim))}
+        # [head, key channel, value channel]: the scan's lanes own value channels, so a key channel's row is read at once.
+        return {"memory": StateSpec((self.num_heads, self.dim, self.vdim))}
 
     def forward_heads(self, x: torch.Tensor, ctx: LayerContext, out: torch.Tensor, out_col: int = 0, scale: float = 1.0) -> None:
         T = x.shape[0]
@@ -152,7 +152,7 @@ class MatrixMemory(_MatrixStateMixer):
 
     def state_spec(self):
         H = self.num_heads
-        return {"memory": StateSpec((H, self.vdim, self.dim)), "normalizer": StateSpec((H, self.dim)), "maximum": StateSpec((H,))}
+        return {"memory": StateSpec((H, self.dim, self.vdim)), "normalizer": StateSpec((H, self.dim)), "maximum": StateSpec((H,))}
 
     def forward_heads(self, x: torch.Tensor, ctx: LayerContext, out: torch.Tensor, out_col: int = 0, scale: float = 1.0) -> None:
         k, ws = ctx.kernels, ctx.workspace

@@ -62,9 +62,9 @@ def test_model_as_data(tmp_path):
     model = load_model(make_libulorn_folder(tmp_path, "A"), "float32", "cpu", max_positions=64)
     entries = model.cache_entries()
     assert len(entries) == 4 and entries[0].kv is None and set(entries[0].state) == {"memory", "normalizer", "maximum"}
-    assert entries[0].state["memory"].shape == (2, 16, 24) and entries[0].state["maximum"].shape == (2,)
+    assert entries[0].state["memory"].shape == (2, 24, 16) and entries[0].state["maximum"].shape == (2,)
     assert (entries[1].kv.num_kv_heads, entries[1].kv.head_dim, entries[1].kv.v_head_dim, entries[1].kv.window) == (2, 16, 24, 11)
-    assert entries[2].kv.window == 16 and set(entries[1].state) == {"right.memory"} and entries[1].state["right.memory"].shape == (3, 16, 8)
+    assert entries[2].kv.window == 16 and set(entries[1].state) == {"right.memory"} and entries[1].state["right.memory"].shape == (3, 8, 16)
     assert entries[3].kv is None and entries[3].state["previous_token"].dtype == "int32"
     cache = CacheManager(entries, page_size=8, num_pages=8, max_slots=3, max_tokens_per_request=64, dtype="float32", device="cpu")
     assert len(cache.groups) == 2 and cache.states[3]["previous_token"].shape == (3,) and cache.states[3]["previous_token"].dtype == torch.int32
@@ -254,7 +254,7 @@ def test_parallel_mixer_sums_its_sides_with_their_scales():
          "left_scale": 1.7, "right_scale": 0.4}
     want = plain.parallel_mixer(x.double(), {k: v.double() for k, v in w.items()}, "m.", m, eps)
     batch, kv = _scenario([(0, T)], part)
-    states = {"right.memory": torch.zeros(2, 3, 8, 4)}
+    states = {"right.memory": torch.zeros(2, 3, 4, 8)}
     assert_close(part.forward(x, _context(batch, kv, states)), want, 1e-5)
 
 

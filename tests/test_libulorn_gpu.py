@@ -86,7 +86,7 @@ def test_gated_linear_scan(kernels, H, D, Dv):
     T = batch.num_tokens
     P = 2 * H * D + H * Dv + 5
     proj, z = _rand(T, P, seed=1), _rand(T, H * D, seed=2, scale=2.0) + 2.0
-    memory = _rand(6, H, Dv, D, seed=3)
+    memory = _rand(6, H, D, Dv, seed=3)
     ref_mem, ref_out = memory.clone(), torch.zeros(T, H * Dv)
     TorchKernels(wide=True).gated_linear_scan(proj, (3, 3 + H * D, 3 + 2 * H * D), z, 7.0, 0.3, batch, ref_mem, ref_out, H, D, Dv)
     got_mem, got_out = memory.clone().to(DEV), torch.zeros(T, H * Dv, device=DEV)
@@ -115,7 +115,7 @@ def test_matrix_memory_scan(kernels, H, D, Dv):
     proj = _rand(T, P, seed=4)
     proj[:, cols[3]:cols[3] + H] = proj[:, cols[3]:cols[3] + H] * 4 - 3        # input gates mostly below the maximum's start, some far above
     proj[:, cols[4]:cols[4] + H] = proj[:, cols[4]:cols[4] + H] * 4 + 2
-    memory, normalizer, maximum = _rand(4, H, Dv, D, seed=5), _rand(4, H, D, seed=6), _rand(4, H, seed=7).abs()
+    memory, normalizer, maximum = _rand(4, H, D, Dv, seed=5), _rand(4, H, D, seed=6), _rand(4, H, seed=7).abs()
     for t in (memory, normalizer, maximum):
         t[0].zero_(), t[1].zero_()                                            # requests that begin in this step
     ref = [memory.clone(), normalizer.clone(), maximum.clone(), torch.zeros(T, H * Dv)]
@@ -142,7 +142,7 @@ def test_scans_in_chunks_side_by_side(kernels, mode, H, D, Dv):
     proj[:, cols[3]:cols[3] + H] = proj[:, cols[3]:cols[3] + H] * 3 - 2
     proj[:, cols[4]:cols[4] + H] = proj[:, cols[4]:cols[4] + H] * 3 + 3
     z = _rand(T, H * D, seed=2, scale=2.0) + 3.0
-    memory, normalizer, maximum = _rand(6, H, Dv, D, seed=5), _rand(6, H, D, seed=6), _rand(6, H, seed=7).abs()
+    memory, normalizer, maximum = _rand(6, H, D, Dv, seed=5), _rand(6, H, D, seed=6), _rand(6, H, seed=7).abs()
     for t in (memory, normalizer, maximum):
         t[1].zero_(), t[2].zero_()
     ref = [memory.clone(), normalizer.clone(), maximum.clone(), torch.zeros(T, H * Dv)]

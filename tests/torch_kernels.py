@@ -299,14 +299,14 @@ class TorchKernels:
         f = self.f
         qc, kc, vc = cols
         for lo, n, slot in self._segments(batch):
-            S = memory[slot].to(f)                                   # [H, Dv, D]
+            S = memory[slot].to(f)                                   # [H, D, Dv]
             for r in range(lo, lo + n):
                 q = proj[r, qc:qc + H * D].to(f).view(H, D) * q_scale
                 k = proj[r, kc:kc + H * D].to(f).view(H, D)
                 v = proj[r, vc:vc + H * Dv].to(f).view(H, Dv)
                 decay = torch.exp(torch.nn.functional.logsigmoid(z[r].to(f)).view(H, D) / tau)
-                S = decay[:, None, :] * S + v[:, :, None] * k[:, None, :]
-                out[r] = torch.einsum("hvd,hd->hv", S, q).reshape(-1).to(out.dtype)
+                S = decay[:, :, None] * S + k[:, :, None] * v[:, None, :]
+                out[r] = torch.einsum("hdv,hd->hv", S, q).reshape(-1).to(out.dtype)
             memory[slot] = S.to(memory.dtype)
 
     def matrix_memory_scan(self, proj, cols, cap, q_scale, floor, batch, memory, normalizer, maximum, out, H, D, Dv, workspace=None):
@@ -322,9 +322,9 @@ class TorchKernels:
                 gf = torch.nn.functional.logsigmoid(cap * torch.tanh(proj[r, fc:fc + H].to(f) / cap))
                 m_new = torch.maximum(gf + m, gi)
                 keep, take = torch.exp(gf + m - m_new), torch.exp(gi - m_new)
-                S = keep[:, None, None] * S + take[:, None, None] * v[:, :, None] * k[:, None, :]
+                S = keep[:, None, None] * S + take[:, None, None] * k[:, :, None] * v[:, None, :]
                 nz = keep[:, None] * nz + take[:, None] * k
                 m = m_new
                 denom = torch.maximum((nz * q).sum(dim=-1).abs(), torch.exp(-m)) + floor
-                out[r] = (torch.einsum("hvd,hd->hv", S, q) / denom[:, None]).reshape(-1).to(out.dtype)
+                out[r] = (torch.einsum("hdv,hd->hv", S, q) / denom[:, None]).reshape(-1).to(out.dtype)
             memory[slot], normalizer[slot], maximum[slot] = S.to(memory.dtype), nz.to(normalizer.dtype), m.to(maximum.dtype)
