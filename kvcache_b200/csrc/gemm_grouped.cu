@@ -26,9 +26,34 @@ struct Shared {
     int failed;
 };
 
-// 32 consecutive accumulator columns of one row on their way to memory; ACT 1: relu(v)^2.
+// 32 consecutive accumulator columns of one row on their way to memory; ACT 1: relu(v)^2.  ACT 2: the columns are
+// (gate, up) pairs and `out` points at the 16 results: g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, +-limit).
 template <int ACT>
-__device__ __forceinline__ void store_chunk(const uint32_t* r, bf16* __restrict__ out, int n, int N) {
+__device__ __forceinline__ void store_chunk(const uint32_t* r, bf16* __restrict__ out, int n, int N, float limit) {
+    if (ACT == 2) {
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float g = fminf(__uint_as_float(r[2 * i]), limit);
+            const float u = fminf(fmaxf(__uint_as_float(r[2 * i + 1]), -limit), limit);
+            v[i] = g / (1.f + __expf(-1.702f * g)) * (u + 1.f);
+        }
+        if (n + 32 <= N && (N & 15) == 0) {
+            uint32_t packed[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                __nv_bfloat162 v2 = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                packed[i] = *reinterpret_cast<uint32_t*>(&v2);
+            }
+            reinterpret_cast<uint4*>(out)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            reinterpret_cast<uint4*>(out)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                if (n + 2 * i + 1 < N) out[i] = __float2bfloat16_rn(v[i]);
+        }
+        return;
+    }
     float v[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
@@ -58,7 +83,8 @@ __device__ __forceinline__ void store_chunk(const uint32_t* r, bf16* __restrict_
 template <int ACT>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, bf16* __restrict__ out,
-                       const int* __restrict__ plan, const int* __restrict__ tile_list, int N, int K, int* __restrict__ err) {
+                       const int* __restrict__ plan, const int* __restrict__ tile_list, int N, int K, float limit,
+                       int* __restrict__ err) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ Shared sh;
@@ -146,7 +172,8 @@ grouped_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + c * 32, r);
                 const int n = n0 + c * 32;
                 if (m >= rows || n >= N) continue;
-                store_chunk<ACT>(r, out + (size_t)(row0 + m) * N + n, n, N);
+                if (ACT == 2) store_chunk<ACT>(r, out + (size_t)(row0 + m) * (N >> 1) + (n >> 1), n, N, limit);
+                else store_chunk<ACT>(r, out + (size_t)(row0 + m) * N + n, n, N, limit);
             }
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
@@ -193,13 +220,13 @@ KVB_API int kvb_gather_rows(const void* x, const int* place, void* xs, int pairs
     return kvb_launch_status();
 }
 
-// a [row_capacity, K] in the plan's order (runs padded to 128 rows), w [experts * N, K], out [row_capacity, N]; `max_tiles`
-// bounds the plan's row tiles.
-KVB_API int kvb_grouped_gemm_tcgen05(const void* a, const void* w, void* out, const int* plan, const int* tile_list, int max_tiles,
-                                     int row_capacity, int experts, int N, int K, int act, int* err, cudaStream_t stream) {
+// a [row_capacity, K] in the plan's order (runs padded to 128 rows), w [experts * N, K], out [row_capacity, N] (act 2:
+// [row_capacity, N / 2]); `max_tiles` bounds the plan's row tiles.
+static int grouped_tcgen05(const void* a, const void* w, void* out, const int* plan, const int* tile_list, int max_tiles,
+                           int row_capacity, int experts, int N, int K, int act, float limit, int* err, cudaStream_t stream) {
     using namespace tc;
     if (max_tiles <= 0) return KVB_OK;
-    if (K % 8 != 0 || N < 1 || act < 0 || act > 1) return KVB_ERR_SHAPE;
+    if (K % 8 != 0 || N < 1 || act < 0 || act > 2 || (act == 2 && N % 2 != 0)) return KVB_ERR_SHAPE;
     if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)out) % 16 != 0) return KVB_ERR_ALIGN;
     CUtensorMap ma, mw;
     int rc = make_bf16_map(&ma, a, row_capacity, K, K, BM);
@@ -211,14 +238,30 @@ KVB_API int kvb_grouped_gemm_tcgen05(const void* a, const void* w, void* out, co
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(grouped_tcgen05_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(grouped_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(grouped_tcgen05_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     const long long tiles = (long long)max_tiles * ((N + BN - 1) / BN);
     const int blocks = tiles < sm_count() ? (int)tiles : sm_count();
-    if (act == 1)
-        grouped_tcgen05_kernel<1><<<blocks, THREADS, smem, stream>>>(ma, mw, (bf16*)out, plan, tile_list, N, K, err);
+    if (act == 2)
+        grouped_tcgen05_kernel<2><<<blocks, THREADS, smem, stream>>>(ma, mw, (bf16*)out, plan, tile_list, N, K, limit, err);
+    else if (act == 1)
+        grouped_tcgen05_kernel<1><<<blocks, THREADS, smem, stream>>>(ma, mw, (bf16*)out, plan, tile_list, N, K, limit, err);
     else
-        grouped_tcgen05_kernel<0><<<blocks, THREADS, smem, stream>>>(ma, mw, (bf16*)out, plan, tile_list, N, K, err);
+        grouped_tcgen05_kernel<0><<<blocks, THREADS, smem, stream>>>(ma, mw, (bf16*)out, plan, tile_list, N, K, limit, err);
     return kvb_launch_status();
+}
+
+KVB_API int kvb_grouped_gemm_tcgen05(const void* a, const void* w, void* out, const int* plan, const int* tile_list, int max_tiles,
+                                     int row_capacity, int experts, int N, int K, int act, int* err, cudaStream_t stream) {
+    if (act > 1) return KVB_ERR_SHAPE;
+    return grouped_tcgen05(a, w, out, plan, tile_list, max_tiles, row_capacity, experts, N, K, act, 0.f, err, stream);
+}
+
+// The same with the activation's constant: act 2 is the clamped gated activation of (gate, up) column pairs with `limit`.
+KVB_API int kvb_grouped_gemm_tcgen05_act(const void* a, const void* w, void* out, const int* plan, const int* tile_list,
+                                         int max_tiles, int row_capacity, int experts, int N, int K, int act, float limit, int* err,
+                                         cudaStream_t stream) {
+    return grouped_tcgen05(a, w, out, plan, tile_list, max_tiles, row_capacity, experts, N, K, act, limit, err, stream);
 }

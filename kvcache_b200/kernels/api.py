@@ -139,6 +139,8 @@ _SIGNATURES = {
         "kvb_gather_rows": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
         "kvb_grouped_gemm_tcgen05": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                                      _c_int, _c_void_p, _c_void_p],
+        "kvb_grouped_gemm_tcgen05_act": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                         _c_int, _c_float, _c_void_p, _c_void_p],
     },
     "moe": {
         "kvb_route_top": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
@@ -950,7 +952,8 @@ class CudaKernels(KernelSet):
 
     def _routed_general(self, x, w_up, w_down, chosen, share, out, act: int, limit: float, base, ws) -> None:
         """The routed feed-forward with any of the grouped product's activations and an optional base: plan, product up
-        (rows gathered, activation in the epilogue), product down, combine - float32 on CUDA cores, bfloat16 on `mma.sync`."""
+        (rows gathered, activation in the epilogue), product down, combine - float32 on CUDA cores, bfloat16 on `mma.sync`,
+        and from `routed_tcgen05_min_pairs` pairs on through the tensor-memory kernel."""
         T, H = x.shape
         E, N, _ = w_up.shape
         F = N // 2 if act == 2 else N
@@ -958,11 +961,35 @@ class CudaKernels(KernelSet):
         pairs = T * top
         i32 = torch.int32
         code, stream = _dtype_code(x.dtype), self._stream()
-        BM = 16 if pairs <= self.ROUTED_SMALL_PAIRS else 64
-        max_tiles = -(-pairs // BM) + E
         place = ws.buffer("moe.place", (pairs,), i32)
         order = ws.buffer("moe.order", (pairs,), i32)
         plan = ws.buffer("moe.plan", (4,), i32)
+        if (self.routed_tcgen05_min_pairs is not None and pairs >= self.routed_tcgen05_min_pairs and x.dtype == torch.bfloat16
+                and H % 8 == 0 and F % 8 == 0 and N % 16 == 0):
+            # Many rows: runs padded to tiles of 128 rows, the step's rows gathered into that order, both products on tcgen05.
+            BM = 128
+            max_tiles = -(-pairs // BM) + E
+            capacity = max_tiles * BM
+            tiles = ws.buffer("moe.tiles", (max_tiles * 3,), i32)
+            xs = ws.buffer("moe.xs", (capacity, H), x.dtype)
+            hidden = ws.buffer("moe.act", (capacity, F), x.dtype)
+            y = ws.buffer("moe.y", (capacity, H), x.dtype)
+            self._count("routed_plan")
+            _check(self._moe.kvb_routed_plan(_ptr(chosen), pairs, E, BM, 1, _ptr(place), _ptr(order), _ptr(plan), _ptr(tiles), stream),
+                   "routed_plan")
+            self._count("gather_rows")
+            _check(self._gemm_grouped.kvb_gather_rows(_ptr(x), _ptr(place), _ptr(xs), pairs, top, H, stream), "gather_rows")
+            for a, w, out_, n, k, act_code, what in ((xs, w_up, hidden, N, H, act, "up"), (hidden, w_down, y, H, F, 0, "down")):
+                self._count("grouped_gemm_tcgen05")
+                _check(self._gemm_grouped.kvb_grouped_gemm_tcgen05_act(_ptr(a), _ptr(w), _ptr(out_), _ptr(plan), _ptr(tiles), max_tiles,
+                                                                       capacity, E, n, k, act_code, limit, _ptr(self.error_word),
+                                                                       stream), f"grouped_gemm_tcgen05 ({what})")
+            self._count("routed_combine")
+            _check(self._moe.kvb_routed_combine_base(code, _ptr(y), _ptr(place), _ptr(share), _ptr(base), _ptr(out), T, top, H, stream),
+                   "routed_combine")
+            return
+        BM = 16 if pairs <= self.ROUTED_SMALL_PAIRS else 64
+        max_tiles = -(-pairs // BM) + E
         tiles = ws.buffer("moe.tiles", (max_tiles * 3,), i32)
         hidden = ws.buffer("moe.act", (pairs, F), x.dtype)
         y = ws.buffer("moe.y", (pairs, H), x.dtype)

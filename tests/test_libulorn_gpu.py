@@ -268,7 +268,8 @@ def test_route_top_with_scores_over_all_experts(kernels, E, top):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,E,top,F,H,with_base", [(9, 5, 2, 24, 40, True), (3, 4, 4, 16, 96, False), (300, 9, 3, 40, 120, True), (1, 16, 2, 64, 256, True)])
+@pytest.mark.parametrize("T,E,top,F,H,with_base", [(9, 5, 2, 24, 40, True), (3, 4, 4, 16, 96, False), (300, 9, 3, 40, 120, True), (1, 16, 2, 64, 256, True),
+                                                   (700, 6, 2, 72, 128, True), (1100, 16, 1, 200, 64, False)])
 def test_routed_experts_with_the_clamped_gated_activation(kernels, dtype, T, E, top, F, H, with_base):
     from kvcache_b200.engine.workspace import Workspace
     x = _rand(T, H, dtype=dtype, seed=1)
