@@ -323,14 +323,16 @@ KVB_API int kvb_qkv_rope_append(int dtype, const void* qkv, const float* bias, c
 // [Hq heads of D | Hkv heads of D | Hkv heads of Dv | ...] with stride `row_stride`.  A query or key head becomes
 // x / sqrt(mean(x^2) + eps) * w (w: D numbers shared by the heads; null: as it is), then its first 2 * rot_half numbers
 // are rotated.  One block per row, a warp per head in turn; the normalised head passes through shared memory so that a
-// lane finds its rotation partner.  Value pages are [pages, Hkv, page_size, Dv].
+// lane finds its rotation partner.  Value pages are [pages, Hkv, page_size, Dv].  `Dk` >= D: queries and keys are stored
+// Dk wide with zeros after their D numbers (keys as wide as values, so that kernels for equal sizes serve them; the
+// zeros add nothing to a score).
 template <typename T>
 __global__ void qkv_norm_rope_append_kernel(const T* __restrict__ qkv, int row_stride, const float* __restrict__ bias,
                                             const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
                                             const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_half,
                                             int table_len, const int* __restrict__ positions, const int* __restrict__ row_segment,
                                             const int* __restrict__ block_table, int table_stride, T* __restrict__ k_pages,
-                                            T* __restrict__ v_pages, T* __restrict__ q_out, int Hq, int Hkv, int D, int Dv,
+                                            T* __restrict__ v_pages, T* __restrict__ q_out, int Hq, int Hkv, int D, int Dv, int Dk,
                                             int page_size, int write_kv, int* __restrict__ err) {
     extern __shared__ float head_s[];          // [warps][D]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
@@ -368,11 +370,11 @@ __global__ void qkv_norm_rope_append_kernel(const T* __restrict__ qkv, int row_s
             for (int d = lane; d < D; d += 32) mine[d] = mine[d] * inv * w[d];
         __syncwarp();
         T* dst = nullptr;
-        if (head < Hq) dst = q_out + ((size_t)r * Hq + head) * D;
-        else if (page_row >= 0) dst = k_pages + ((size_t)page_row + (size_t)(head - Hq) * page_size) * D;
+        if (head < Hq) dst = q_out + ((size_t)r * Hq + head) * Dk;
+        else if (page_row >= 0) dst = k_pages + ((size_t)page_row + (size_t)(head - Hq) * page_size) * Dk;
         if (dst)
-            for (int d = lane; d < D; d += 32) {
-                float v = mine[d];
+            for (int d = lane; d < Dk; d += 32) {
+                float v = d < D ? mine[d] : 0.f;
                 if (d < 2 * rot_half) {
                     const bool low = d < rot_half;
                     const int t = low ? d : d - rot_half;
@@ -397,9 +399,10 @@ KVB_API int kvb_qkv_norm_rope_append(int dtype, const void* qkv, int row_stride,
                                      const float* k_w, float eps, const float* cos_t, const float* sin_t, int rot_half,
                                      int table_len, const int* positions, const int* row_segment, const int* block_table,
                                      int table_stride, void* k_pages, void* v_pages, void* q_out, int T, int Hq, int Hkv, int D,
-                                     int Dv, int page_size, int write_kv, int* err, cudaStream_t stream) {
+                                     int Dv, int Dk, int page_size, int write_kv, int* err, cudaStream_t stream) {
     if (T <= 0) return KVB_OK;
-    if (2 * rot_half > D || rot_half < 0 || Dv < 1 || row_stride < (Hq + Hkv) * D + Hkv * Dv || (q_w == nullptr) != (k_w == nullptr))
+    if (2 * rot_half > D || rot_half < 0 || Dv < 1 || Dk < D || row_stride < (Hq + Hkv) * D + Hkv * Dv ||
+        (q_w == nullptr) != (k_w == nullptr))
         return KVB_ERR_SHAPE;
     const int warps = Hq + Hkv >= 8 ? 8 : 4;
     const size_t smem = (size_t)warps * D * sizeof(float);
@@ -407,11 +410,11 @@ KVB_API int kvb_qkv_norm_rope_append(int dtype, const void* qkv, int row_stride,
     if (dtype == KVB_F32)
         kvb_launch(qkv_norm_rope_append_kernel<float>, dim3(T), dim3(32 * warps), smem, stream, (const float*)qkv, row_stride, bias,
                    q_w, k_w, eps, cos_t, sin_t, rot_half, table_len, positions, row_segment, block_table, table_stride,
-                   (float*)k_pages, (float*)v_pages, (float*)q_out, Hq, Hkv, D, Dv, page_size, write_kv, err);
+                   (float*)k_pages, (float*)v_pages, (float*)q_out, Hq, Hkv, D, Dv, Dk, page_size, write_kv, err);
     else if (dtype == KVB_BF16)
         kvb_launch(qkv_norm_rope_append_kernel<bf16>, dim3(T), dim3(32 * warps), smem, stream, (const bf16*)qkv, row_stride, bias,
                    q_w, k_w, eps, cos_t, sin_t, rot_half, table_len, positions, row_segment, block_table, table_stride,
-                   (bf16*)k_pages, (bf16*)v_pages, (bf16*)q_out, Hq, Hkv, D, Dv, page_size, write_kv, err);
+                   (bf16*)k_pages, (bf16*)v_pages, (bf16*)q_out, Hq, Hkv, D, Dv, Dk, page_size, write_kv, err);
     else
         return KVB_ERR_DTYPE;
     return kvb_launch_status();

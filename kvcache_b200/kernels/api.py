@@ -98,7 +98,7 @@ _SIGNATURES = {
                                 _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
         "kvb_qkv_norm_rope_append": [_c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_int,
                                      _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
-                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     },
     "recurrent": {
         "kvb_matrix_state_scan": [_c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_float,
@@ -608,21 +608,24 @@ class CudaKernels(KernelSet):
     def qkv_rope_append(self, qkv: torch.Tensor, bias: Optional[torch.Tensor], cos: Optional[torch.Tensor],
                         sin: Optional[torch.Tensor], batch: StepBatch, kv: PagedKVView, q_out: torch.Tensor,
                         num_heads: int, q_norm: Optional[torch.Tensor] = None, k_norm: Optional[torch.Tensor] = None,
-                        norm_eps: float = 0.0) -> None:
-        """`q_norm` / `k_norm` (float32 [head_dim]): queries and keys are divided by their root mean square per head and
+                        norm_eps: float = 0.0, key_dim: Optional[int] = None) -> None:
+        """`q_norm` / `k_norm` (float32 [key_dim]): queries and keys are divided by their root mean square per head and
         multiplied by these before the rotation.  Values may have another size than keys (`kv.spec.v_head_dim`), and rows
-        of `qkv` may carry further columns after [q | k | v]."""
+        of `qkv` may carry further columns after [q | k | v].  `key_dim` < `kv.spec.head_dim`: queries and keys have
+        `key_dim` numbers in `qkv` and are stored `kv.spec.head_dim` wide, with zeros after them."""
         T = qkv.shape[0]
         spec = kv.spec
         rot_half = 0 if cos is None else cos.shape[1]
         table_len = 0 if cos is None else cos.shape[0]
-        if q_norm is not None or spec.v_head_dim != spec.head_dim or qkv.shape[1] != (num_heads + 2 * spec.num_kv_heads) * spec.head_dim:
+        D = spec.head_dim if key_dim is None else int(key_dim)
+        if (q_norm is not None or spec.v_head_dim != spec.head_dim or D != spec.head_dim
+                or qkv.shape[1] != (num_heads + 2 * spec.num_kv_heads) * spec.head_dim):
             self._count("norm_rope_append")
             _check(self._rope.kvb_qkv_norm_rope_append(
                 _dtype_code(qkv.dtype), _ptr(qkv), qkv.shape[1], _ptr(bias), _ptr(q_norm), _ptr(k_norm), float(norm_eps), _ptr(cos),
                 _ptr(sin), rot_half, table_len, _ptr(batch.positions), _ptr(batch.row_segment), _ptr(kv.block_table),
                 kv.block_table.shape[1], _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(q_out), T, num_heads, spec.num_kv_heads,
-                spec.head_dim, spec.v_head_dim, kv.page_size, 1 if kv.writes else 0, _ptr(self.error_word), self._stream()),
+                D, spec.v_head_dim, spec.head_dim, kv.page_size, 1 if kv.writes else 0, _ptr(self.error_word), self._stream()),
                 "qkv_norm_rope_append")
             return
         self._count("rope_append")

@@ -47,6 +47,13 @@ class GQAAttention(Mixer):
         self.heads_width = num_heads * self.value_dim        # what the output matrix multiplies
         # The plain layer (equal key and value sizes, no norm of q and k, no gate) has fused and folded forms.
         self.plain = self.value_dim == head_dim and self.qk_norm_eps is None and head_gate is None
+        # Keys narrower than values are cached as wide as the values, with zeros after their numbers (which add nothing
+        # to a score), where that brings the layer to the tensor-core attention kernels, which take one size for both:
+        # bfloat16, values of up to 128 numbers in steps of 16.  The cache then holds 2 value_dim numbers a token and
+        # key/value head instead of head_dim + value_dim.
+        self.key_store = head_dim
+        if dtype == "bfloat16" and head_dim < self.value_dim <= 128 and self.value_dim % 16 == 0 and num_heads // num_kv_heads <= 16:
+            self.key_store = self.value_dim
         self.w_qkv: Optional[torch.Tensor] = None
         self.b_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
@@ -124,8 +131,8 @@ class GQAAttention(Mixer):
         return self.w_o
 
     def cache_spec(self) -> PagedKVSpec:
-        return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window,
-                           None if self.value_dim == self.head_dim else self.value_dim)
+        return PagedKVSpec(self.num_kv_heads, self.key_store, self.window,
+                           None if self.value_dim == self.key_store else self.value_dim)
 
     def step_planners(self, kernels):
         planner = getattr(kernels, "paged_attention_planner", None)
@@ -160,9 +167,9 @@ class GQAAttention(Mixer):
         k.linear(x, self.w_qkv, qkv)
         rotation = self.position.rotation() if self.position is not None else None
         cos, sin = (rotation.cos, rotation.sin) if rotation else (None, None)
-        q = ws.buffer("attn.q", (T, self.q_size), self.dtype)
+        q = ws.buffer("attn.q", (T, self.num_heads * self.key_store), self.dtype)
         k.qkv_rope_append(qkv, self.b_qkv, cos, sin, ctx.batch, ctx.kv, q, self.num_heads, q_norm=self.q_norm, k_norm=self.k_norm,
-                          norm_eps=self.qk_norm_eps or 0.0)
+                          norm_eps=self.qk_norm_eps or 0.0, key_dim=self.head_dim)
         direct = self.head_gate is None and scale == 1.0 and out_col == 0 and out.shape[1] == self.heads_width
         attn = out if direct else ws.buffer("attn.out", (T, self.heads_width), self.dtype)
         k.paged_attention(q, ctx.batch, ctx.kv, attn, self.num_heads, self.scale, ws)

@@ -211,6 +211,53 @@ def _two_size_scenario(segments, Hkv, D, Dv, page, dtype, window, seed=2):
                               v_pages=_rand(*kv.k_pages.shape[:-1], Dv, dtype=dtype, seed=seed + 1), block_table=kv.block_table, page_size=page, writes=True)
 
 
+def test_keys_stored_as_wide_as_values(kernels):
+    """bfloat16, keys of 40 numbers beside values of 64: queries and keys are stored 64 wide with zeros after their
+    numbers, and the attention kernels for one size give what the plain statement gives for two."""
+    from kvcache_b200.engine.workspace import Workspace
+    from kvcache_b200.parts.base import PagedKVSpec, PagedKVView
+    Hq, Hkv, D, Dv, dtype = 6, 2, 40, 64, torch.bfloat16
+    segments = [(0, 45), (130, 1), (30, 20)]
+    batch, two = _two_size_scenario(segments, Hkv, D, Dv, 8, dtype, 33)
+    two.k_pages.zero_(), two.v_pages.zero_()
+    wide = PagedKVView(spec=PagedKVSpec(Hkv, Dv, 33), k_pages=torch.zeros(*two.k_pages.shape[:-1], Dv, dtype=dtype), v_pages=two.v_pages.clone(),
+                       block_table=two.block_table, page_size=8, writes=True)
+    T = batch.num_tokens
+    # The cached part of every request first (as one prompt each), then the step itself; both layouts side by side.
+    history = [(0, s) for s, _ in segments if s > 0]
+    hist_batch, _ = _two_size_scenario(history, Hkv, D, Dv, 8, dtype, 33)
+    rows = [i for i, (s, _) in enumerate(segments) if s > 0]
+    hist_table = two.block_table[rows]
+    qw, kw = 1 + _rand(D, seed=8, scale=0.3), 1 + _rand(D, seed=9, scale=0.3)
+    ang = torch.arange(200, dtype=torch.float64)[:, None] * torch.logspace(0, -3, 8, dtype=torch.float64)[None, :]
+    cos, sin = torch.cos(ang).float(), torch.sin(ang).float()
+    outs = {}
+    for name, view in (("two", two), ("wide", wide)):
+        for step_batch, table, seed in ((hist_batch, hist_table, 1), (batch, two.block_table, 2)):
+            n = step_batch.num_tokens
+            qkv = _rand(n, (Hq + Hkv) * D + Hkv * Dv + Hq, dtype=dtype, seed=seed, scale=2.0)
+            kv = PagedKVView(spec=view.spec, k_pages=view.k_pages, v_pages=view.v_pages, block_table=table, page_size=8, writes=True)
+            if name == "two":
+                q = torch.zeros(n, Hq * D, dtype=dtype)
+                TorchKernels(wide=True).qkv_rope_append(qkv, None, cos, sin, step_batch, kv, q, Hq, q_norm=qw, k_norm=kw, norm_eps=1e-5)
+                out = torch.zeros(n, Hq * Dv, dtype=dtype)
+                TorchKernels(wide=True).paged_attention(q, step_batch, kv, out, Hq, 0.3)
+            else:
+                dev_kv = PagedKVView(spec=view.spec, k_pages=view.k_pages.to(DEV), v_pages=view.v_pages.to(DEV), block_table=table.to(DEV), page_size=8, writes=True)
+                q = torch.zeros(n, Hq * Dv, dtype=dtype, device=DEV)
+                kernels.qkv_rope_append(qkv.to(DEV), None, cos.to(DEV), sin.to(DEV), batch_to(step_batch, DEV), dev_kv, q, Hq, q_norm=qw.to(DEV),
+                                        k_norm=kw.to(DEV), norm_eps=1e-5, key_dim=D)
+                assert float(q.view(n, Hq, Dv)[:, :, D:].abs().max()) == 0
+                out = torch.zeros(n, Hq * Dv, dtype=dtype, device=DEV)
+                kernels.paged_attention(q, batch_to(step_batch, DEV), dev_kv, out, Hq, 0.3, Workspace(DEV))
+                view.k_pages.copy_(dev_kv.k_pages.cpu()), view.v_pages.copy_(dev_kv.v_pages.cpu())
+            outs[name] = out
+    kernels.check_errors()
+    assert_close(outs["wide"], outs["two"], 2e-2)
+    assert_close(wide.k_pages[..., :D], two.k_pages, 2e-2, "keys")
+    assert float(wide.k_pages[..., D:].abs().max()) == 0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("Hq,Hkv,D,Dv,window", [(4, 2, 16, 24, 11), (3, 3, 6, 2, None), (8, 4, 96, 192, 96), (5, 1, 40, 72, 16), (2, 1, 64, 32, 1)])
 def test_attention_with_values_of_another_size_than_keys(kernels, dtype, Hq, Hkv, D, Dv, window):

@@ -48,15 +48,15 @@ class TorchKernels:
             y = y + bias.to(self.f)
         out.copy_(y.to(out.dtype))
 
-    def qkv_rope_append(self, qkv, bias, cos, sin, batch, kv, q_out, num_heads, q_norm=None, k_norm=None, norm_eps=0.0):
+    def qkv_rope_append(self, qkv, bias, cos, sin, batch, kv, q_out, num_heads, q_norm=None, k_norm=None, norm_eps=0.0, key_dim=None):
         f = self.f
         T = qkv.shape[0]
         Hq, Hkv, D = num_heads, kv.spec.num_kv_heads, kv.spec.head_dim
         x = qkv.to(f)
         if bias is not None:
             x = x + bias.to(f)
-        if q_norm is not None or kv.spec.v_head_dim != D or x.shape[1] != (Hq + 2 * Hkv) * D:
-            return self._qkv_norm_rope_append(x, cos, sin, batch, kv, q_out, Hq, q_norm, k_norm, norm_eps)
+        if q_norm is not None or kv.spec.v_head_dim != D or x.shape[1] != (Hq + 2 * Hkv) * D or (key_dim or D) != D:
+            return self._qkv_norm_rope_append(x, cos, sin, batch, kv, q_out, Hq, q_norm, k_norm, norm_eps, key_dim or D)
         x = x.view(T, Hq + 2 * Hkv, D).clone()
         pos = batch.positions.long()
         if cos is not None:
@@ -75,11 +75,12 @@ class TorchKernels:
             kv.k_pages[page, :, slot, :] = x[:, Hq:Hq + Hkv, :].to(kv.k_pages.dtype)
             kv.v_pages[page, :, slot, :] = x[:, Hq + Hkv:, :].to(kv.v_pages.dtype)
 
-    def _qkv_norm_rope_append(self, x, cos, sin, batch, kv, q_out, Hq, q_norm, k_norm, eps):
-        """Rows [q heads of D | k heads of D | v heads of Dv | columns that are not this operator's]."""
+    def _qkv_norm_rope_append(self, x, cos, sin, batch, kv, q_out, Hq, q_norm, k_norm, eps, D):
+        """Rows [q heads of D | k heads of D | v heads of Dv | columns that are not this operator's]; queries and keys are
+        stored kv.spec.head_dim wide, with zeros after their D numbers."""
         f = self.f
         T = x.shape[0]
-        Hkv, D, Dv = kv.spec.num_kv_heads, kv.spec.head_dim, kv.spec.v_head_dim
+        Hkv, Dv, wide = kv.spec.num_kv_heads, kv.spec.v_head_dim, kv.spec.head_dim
         q = x[:, :Hq * D].reshape(T, Hq, D).clone()
         k = x[:, Hq * D:(Hq + Hkv) * D].reshape(T, Hkv, D).clone()
         v = x[:, (Hq + Hkv) * D:(Hq + Hkv) * D + Hkv * Dv].reshape(T, Hkv, Dv)
@@ -93,7 +94,10 @@ class TorchKernels:
             for t in (q, k):
                 u, w = t[..., :half].clone(), t[..., half:2 * half].clone()
                 t[..., :half], t[..., half:2 * half] = u * c - w * s, w * c + u * s
-        q_out.copy_(q.reshape(T, Hq * D).to(q_out.dtype))
+        if wide > D:
+            q = torch.cat([q, torch.zeros(T, Hq, wide - D, dtype=f)], dim=-1)
+            k = torch.cat([k, torch.zeros(T, Hkv, wide - D, dtype=f)], dim=-1)
+        q_out.copy_(q.reshape(T, Hq * wide).to(q_out.dtype))
         if kv.writes:
             page = kv.block_table[batch.row_segment.long(), pos // kv.page_size].long()
             assert bool((page >= 0).all()), "append into a page the block table does not hold"
