@@ -454,14 +454,14 @@ def libulorn_sizes():
             ("0.5B-like-wide-values", "0.5B-like", 896, 7, 1, 64, 128, 7, 64, 128, 4864, 16, 2, 32768),
             ("3B-like", "3B-like", 2048, 16, 2, 128, 128, 8, 128, 256, 11008, 32, 4, 32768)):
         left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "mask": {"size": 1024},
-                "rot": {"base": 10000.0, "dims": dim // 2, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 2048}}}
-        right = {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "tau": 16.0, "decay_rank": 16}
+                "rot": {"base": 500000.0, "dims": dim // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+        right = {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "tau": 8.0, "decay_rank": 32}
         mlp = {"kind": "moe", "expert": {"ff": ff // (2 * top) // 16 * 16, "limit": 7.0}, "router": {"experts": experts, "top": top},
                "shared": {"ff": ff // 2, "limit": 7.0}}
         parallel = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}, "mlp": mlp}
-        memory = {"type": "mlstm", "mixer": {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "gate_cap": 15.0}, "mlp": mlp}
+        memory = {"type": "mlstm", "mixer": {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "gate_cap": 10.0}, "mlp": mlp}
         lib = {"architecture": "Libulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
-               "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+               "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 257}},
                "layers": [parallel, memory, parallel, memory], "initializer_range": 0.02}
         out.append((name, {"libulorn": lib, "kakipel": others[like][0], "qwen2": others[like][1]}))
     return out

@@ -69,7 +69,7 @@ LIB_B = {
 LIB_C = {
     "architecture": "Libulorn", "vocab": 150, "width": 40, "norm": {"eps": 1e-5},
     "layers": [
-        _layer(_memory(3, 12, 20, 15.0), _moe(2, 1, 56, 2.0, (24, 1.0))),
+        _layer(_memory(3, 12, 20, 12.0), _moe(2, 1, 56, 2.0, (24, 1.0))),
         _layer(_memory(5, 8, 8, 1.0), None),
     ],
 }

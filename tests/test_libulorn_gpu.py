@@ -175,7 +175,7 @@ def test_head_norm_gate_and_head_gate(kernels, dtype, H, Dv, per_head, act):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("Hq,Hkv,D,Dv,rot", [(4, 2, 16, 24, 8), (3, 3, 6, 2, 6), (8, 4, 96, 192, 24), (5, 1, 40, 40, 0), (2, 2, 128, 64, 128)])
+@pytest.mark.parametrize("Hq,Hkv,D,Dv,rot", [(4, 2, 16, 24, 8), (3, 3, 6, 2, 6), (6, 3, 80, 160, 40), (5, 1, 40, 40, 0), (2, 2, 128, 64, 128)])
 def test_norm_rotation_append_with_two_sizes(kernels, dtype, Hq, Hkv, D, Dv, rot):
     from kvcache_b200.parts.base import PagedKVSpec, PagedKVView
     segments = [(0, 5), (37, 1), (14, 20)]
@@ -259,7 +259,7 @@ def test_keys_stored_as_wide_as_values(kernels):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("Hq,Hkv,D,Dv,window", [(4, 2, 16, 24, 11), (3, 3, 6, 2, None), (8, 4, 96, 192, 96), (5, 1, 40, 72, 16), (2, 1, 64, 32, 1)])
+@pytest.mark.parametrize("Hq,Hkv,D,Dv,window", [(4, 2, 16, 24, 11), (3, 3, 6, 2, None), (6, 3, 80, 160, 70), (5, 1, 40, 72, 16), (2, 1, 64, 32, 1)])
 def test_attention_with_values_of_another_size_than_keys(kernels, dtype, Hq, Hkv, D, Dv, window):
     from kvcache_b200.engine.workspace import Workspace
     batch, kv = _two_size_scenario([(0, 45), (130, 1), (30, 20), (16, 1)], Hkv, D, Dv, 8, dtype, window)
@@ -315,7 +315,7 @@ def test_route_top_with_scores_over_all_experts(kernels, E, top):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,E,top,F,H,with_base", [(9, 5, 2, 24, 40, True), (3, 4, 4, 16, 96, False), (300, 9, 3, 40, 120, True), (1, 16, 2, 64, 256, True),
+@pytest.mark.parametrize("T,E,top,F,H,with_base", [(9, 5, 2, 24, 40, True), (3, 4, 4, 16, 96, False), (300, 9, 3, 40, 120, True), (1, 12, 2, 48, 192, True),
                                                    (700, 6, 2, 72, 128, True), (1100, 16, 1, 200, 64, False)])
 def test_routed_experts_with_the_clamped_gated_activation(kernels, dtype, T, E, top, F, H, with_base):
     from kvcache_b200.engine.workspace import Workspace
