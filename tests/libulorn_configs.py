@@ -82,8 +82,18 @@ LIB_D = {
         _layer(_parallel(_attention(10, 2, 8, 16, 0.35, 37, (300000.0, 8, (2.5, 2.0, 8.0, 64))), (4, 16, 8, 2.0, 4), 0.9, 1.2), _moe(9, 3, 40, 1.0, (72, 4.0))),
     ],
 }
-CONFIGS = {"A": LIB_A, "B": LIB_B, "C": LIB_C, "D": LIB_D}
-PAGE_SIZE = {"A": 8, "B": 16, "C": 16, "D": 4}
+# E: sizes in steps of 16 as real models have them - keys of 64 beside values of 128 (in bfloat16 the keys are cached as
+# wide as the values and the layer runs on the tensor-core attention kernels), a window that crosses pages.
+LIB_E = {
+    "architecture": "Libulorn", "vocab": 300, "width": 128, "norm": {"eps": 1e-6},
+    "embedding": {"bigram": {"buckets": 211, "mul_prev": 17, "mul_cur": 3}},
+    "layers": [
+        _layer(_parallel(_attention(4, 2, 64, 128, 0.125, 40, (50000.0, 32, (8.0, 1.0, 4.0, 256))), (2, 32, 64, 8.0, 8), 1.1, 0.8), _moe(4, 2, 32, 2.0, (64, 1.5))),
+        _layer(_memory(2, 32, 64, 10.0), _moe(4, 2, 32, 2.0, (64, 1.5))),
+    ],
+}
+CONFIGS = {"A": LIB_A, "B": LIB_B, "C": LIB_C, "D": LIB_D, "E": LIB_E}
+PAGE_SIZE = {"A": 8, "B": 16, "C": 16, "D": 4, "E": 16}
 
 
 def config_dict(name: str, **changes) -> dict:

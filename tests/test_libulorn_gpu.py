@@ -409,6 +409,23 @@ def test_long_prompts_whose_states_are_scanned_in_chunks(tmp_path, kernels, name
     assert_close(more[267:], plain.logits_of(config, weights, other)[-1:], 2e-4, "the other request")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_prompts_through_the_tensor_core_attention_with_keys_stored_wide(tmp_path, kernels, dtype):
+    """Keys of 64 beside values of 128: in bfloat16 the cache entry is 128 wide and a portion of 384 rows and more runs
+    on the tensor-memory attention kernel, shorter ones and decoded tokens on the other tensor-core kernels, all with
+    the window; in float32 the two-size kernel.  Whole, in portions that straddle the kernels' row limit, then decoded."""
+    runner, config, weights = _runner(tmp_path, kernels, "E", dtype, num_pages=48, max_tokens_per_step=640, max_tokens_per_request=640)
+    spec = runner.model.blocks[0].mixer.cache_spec()
+    assert (spec.head_dim, spec.v_head_dim) == ((128, 128) if dtype == "bfloat16" else (64, 128))
+    tokens = random_tokens(config["vocab"], 520, 21)
+    want = plain.logits_of(config, weights, tokens)
+    spread = _spread(config, weights, tokens, want) if dtype == "bfloat16" else None
+    assert_model_close(replay_modes.whole(runner, tokens), want, dtype, "whole", spread, 2e-4)
+    assert_model_close(replay_modes.portions(runner, tokens, [400, 3, 100, 17]), want, dtype, "portions", spread, 2e-4)
+    assert_model_close(replay_modes.portions(runner, tokens, [450] + [1] * 70), want, dtype, "decoded", spread, 2e-4)
+    kernels.check_errors()
+
+
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_float32_rows_do_not_depend_on_the_batch_or_the_cut(tmp_path, kernels, name):
     """In float32 a position's logits are bit for bit the same alone, beside other requests, and in portions."""
