@@ -36,6 +36,15 @@ template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
 
+// The gated activation in the epilogues of the products over interleaved gate/up rows.  limit <= 0: silu(g) * u.
+// limit > 0: g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit).
+__device__ __forceinline__ float gated_pair(float g, float u, float limit) {
+    if (limit <= 0.f) return g / (1.f + expf(-g)) * u;
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -80,6 +80,7 @@ struct Fused {
     bf16* q_out;              // [M, Hq * D]
     int* err;
     int table_len, table_stride, Hq, Hkv, D, page_size, page_shift, writes;
+    float act_limit;          // EPI_ACT: 0 - silu(g) * u; > 0 - the clamped gated activation with this limit (common.cuh)
 };
 
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
@@ -360,7 +361,7 @@ __global__ void __maxnreg__((RT == 1 && NT <= 2) ? 96 : 255) gemm_skinny_kernel(
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const float gate = vals[e], up = vals[e + 2];
-                    if (m + e < M) y[(size_t)(m + e) * I + i] = from_f32<TOut>(gate / (1.f + expf(-gate)) * up);
+                    if (m + e < M) y[(size_t)(m + e) * I + i] = from_f32<TOut>(gated_pair(gate, up, fz.act_limit));
                 }
             }
         } else if (EPI == EPI_RESID) {
@@ -524,8 +525,8 @@ int dispatch(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, in
 // x: [M, K] bfloat16; w: [N, K] bfloat16; bias: float32 [N] or null; y: [M, N] bfloat16 (out_dtype 1) or float32
 // (out_dtype 0) - or, with swiglu = 1, [M, N / 2] from interleaved gate/up rows (N a multiple of 16, no bias).
 // Refuses M > 64, K not a multiple of 32, misaligned operands.
-KVB_API int kvb_gemm_skinny(int out_dtype, int act, const void* x, const void* w, const float* bias, void* y, int M,
-                            int N, int K, cudaStream_t stream) {
+static int gemm_skinny(int out_dtype, int act, const void* x, const void* w, const float* bias, void* y, int M, int N, int K,
+                       float act_limit, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return KVB_OK;
     if (M > 64 || K <= 0 || K % 32 != 0) return KVB_ERR_SHAPE;
     if (((uintptr_t)x | (uintptr_t)w) & 15) return KVB_ERR_ALIGN;
@@ -533,7 +534,8 @@ KVB_API int kvb_gemm_skinny(int out_dtype, int act, const void* x, const void* w
     const bf16* wb = (const bf16*)w;
     if (act && (N % 16 != 0 || bias != nullptr)) return KVB_ERR_SHAPE;
     const int x_stride = K;
-    const skinny::Fused none = {};
+    skinny::Fused none = {};
+    none.act_limit = act_limit;
     using namespace skinny;
     if (out_dtype == KVB_BF16)
         return act ? dispatch<EPI_ACT, false, bf16>(xb, wb, bias, (bf16*)y, M, N, K, x_stride, none, stream)
@@ -542,6 +544,18 @@ KVB_API int kvb_gemm_skinny(int out_dtype, int act, const void* x, const void* w
         return act ? dispatch<EPI_ACT, false, float>(xb, wb, bias, (float*)y, M, N, K, x_stride, none, stream)
                    : dispatch<EPI_PLAIN, false, float>(xb, wb, bias, (float*)y, M, N, K, x_stride, none, stream);
     return KVB_ERR_DTYPE;
+}
+
+KVB_API int kvb_gemm_skinny(int out_dtype, int act, const void* x, const void* w, const float* bias, void* y, int M,
+                            int N, int K, cudaStream_t stream) {
+    return gemm_skinny(out_dtype, act, x, w, bias, y, M, N, K, 0.f, stream);
+}
+
+// The gated form with the clamped activation of `limit` > 0 in its epilogue (see gated_pair): y [M, N / 2].
+KVB_API int kvb_gemm_skinny_gated(int out_dtype, const void* x, const void* w, void* y, int M, int N, int K, float limit,
+                                  cudaStream_t stream) {
+    if (!(limit > 0.f)) return KVB_ERR_SHAPE;
+    return gemm_skinny(out_dtype, 1, x, w, nullptr, y, M, N, K, limit, stream);
 }
 
 // The fused forms (M <= 16, bfloat16 throughout).  `x` holds rows of the residual stream rounded to bfloat16 where

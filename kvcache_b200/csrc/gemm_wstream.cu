@@ -42,6 +42,7 @@ struct Params {
     void* y;
     int M, N, K, ksplit;
     int* err;
+    float act_limit;       // gated output: 0 - silu(g) * u; > 0 - the clamped gated activation with this limit (common.cuh)
 };
 
 // MB: rows of x the accumulator holds (32, 64 or 128).
@@ -183,7 +184,7 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     const float up = __shfl_down_sync(0xffffffffu, vals[e], 8);
                     const int m = 4 * j + e;
                     if ((n & 15) < 8 && n + 8 < p.N && m < p.M)
-                        y[(size_t)m * I + i] = from_f32<TOut>(vals[e] / (1.f + expf(-vals[e])) * up);
+                        y[(size_t)m * I + i] = from_f32<TOut>(gated_pair(vals[e], up, p.act_limit));
                 }
             } else {
 #pragma unroll
@@ -242,7 +243,8 @@ static int choose_split(int N, int K) {
 }
 
 template <int MB, typename TOut, bool SWIGLU>
-static int launch(const void* x, const void* w, const float* bias, void* y, int M, int N, int K, int* err, cudaStream_t stream) {
+static int launch(const void* x, const void* w, const float* bias, void* y, int M, int N, int K, int* err, float act_limit,
+                  cudaStream_t stream) {
     CUtensorMap mw, mx;
     int rc = make_map(&mw, w, N, K, BN);
     if (rc != KVB_OK) return rc;
@@ -263,7 +265,7 @@ static int launch(const void* x, const void* w, const float* bias, void* y, int 
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    Params p{bias, y, M, N, K, ksplit, err};
+    Params p{bias, y, M, N, K, ksplit, err, act_limit};
     const int tiles = (N + BN - 1) / BN;
     if (ksplit > 1)
         kvb_launch_cluster(kernel, dim3(tiles * ksplit), dim3(THREADS), (unsigned)ksplit, smem, stream, mw, mx, p);
@@ -273,10 +275,11 @@ static int launch(const void* x, const void* w, const float* bias, void* y, int 
 }
 
 template <typename TOut, bool SWIGLU>
-static int dispatch(const void* x, const void* w, const float* bias, void* y, int M, int N, int K, int* err, cudaStream_t stream) {
-    if (M <= 32) return launch<32, TOut, SWIGLU>(x, w, bias, y, M, N, K, err, stream);
-    if (M <= 64) return launch<64, TOut, SWIGLU>(x, w, bias, y, M, N, K, err, stream);
-    return launch<128, TOut, SWIGLU>(x, w, bias, y, M, N, K, err, stream);
+static int dispatch(const void* x, const void* w, const float* bias, void* y, int M, int N, int K, int* err, float act_limit,
+                    cudaStream_t stream) {
+    if (M <= 32) return launch<32, TOut, SWIGLU>(x, w, bias, y, M, N, K, err, act_limit, stream);
+    if (M <= 64) return launch<64, TOut, SWIGLU>(x, w, bias, y, M, N, K, err, act_limit, stream);
+    return launch<128, TOut, SWIGLU>(x, w, bias, y, M, N, K, err, act_limit, stream);
 }
 
 }  // namespace ws
@@ -284,17 +287,29 @@ static int dispatch(const void* x, const void* w, const float* bias, void* y, in
 // x [M, K], w [N, K] bfloat16 row-major; bias float32 [N] or null; y [M, N] bfloat16 (out_dtype 1) or float32 (0),
 // or with swiglu = 1 [M, N / 2] from interleaved gate/up rows (N % 16 == 0, no bias).
 // Refuses M > 128, K % 8 != 0 and operands that are not 16-byte aligned.
-KVB_API int kvb_gemm_wstream(int out_dtype, int swiglu, const void* x, const void* w, const float* bias, void* y, int M,
-                             int N, int K, int* err, cudaStream_t stream) {
+static int gemm_wstream(int out_dtype, int swiglu, const void* x, const void* w, const float* bias, void* y, int M, int N, int K,
+                        int* err, float act_limit, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return KVB_OK;
     if (M > 128 || K <= 0 || K % 8 != 0) return KVB_ERR_SHAPE;
     if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) return KVB_ERR_ALIGN;
     if (swiglu && (N % 16 != 0 || bias != nullptr)) return KVB_ERR_SHAPE;
     if (out_dtype == KVB_BF16)
-        return swiglu ? ws::dispatch<bf16, true>(x, w, bias, y, M, N, K, err, stream)
-                      : ws::dispatch<bf16, false>(x, w, bias, y, M, N, K, err, stream);
+        return swiglu ? ws::dispatch<bf16, true>(x, w, bias, y, M, N, K, err, act_limit, stream)
+                      : ws::dispatch<bf16, false>(x, w, bias, y, M, N, K, err, act_limit, stream);
     if (out_dtype == KVB_F32)
-        return swiglu ? ws::dispatch<float, true>(x, w, bias, y, M, N, K, err, stream)
-                      : ws::dispatch<float, false>(x, w, bias, y, M, N, K, err, stream);
+        return swiglu ? ws::dispatch<float, true>(x, w, bias, y, M, N, K, err, act_limit, stream)
+                      : ws::dispatch<float, false>(x, w, bias, y, M, N, K, err, act_limit, stream);
     return KVB_ERR_DTYPE;
+}
+
+KVB_API int kvb_gemm_wstream(int out_dtype, int swiglu, const void* x, const void* w, const float* bias, void* y, int M,
+                             int N, int K, int* err, cudaStream_t stream) {
+    return gemm_wstream(out_dtype, swiglu, x, w, bias, y, M, N, K, err, 0.f, stream);
+}
+
+// The gated form with the clamped activation of `limit` > 0 in its epilogue (see gated_pair): y [M, N / 2].
+KVB_API int kvb_gemm_wstream_gated(int out_dtype, const void* x, const void* w, void* y, int M, int N, int K, float limit, int* err,
+                                   cudaStream_t stream) {
+    if (!(limit > 0.f)) return KVB_ERR_SHAPE;
+    return gemm_wstream(out_dtype, 1, x, w, nullptr, y, M, N, K, err, limit, stream);
 }

@@ -158,6 +158,7 @@ _SIGNATURES = {
     },
     "gemm_skinny": {
         "kvb_gemm_skinny": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+        "kvb_gemm_skinny_gated": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p],
         "kvb_gemm_skinny_norm_act": [_c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
         "kvb_gemm_skinny_residual": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
         "kvb_gemm_skinny_qkv": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_int, _c_void_p,
@@ -166,6 +167,7 @@ _SIGNATURES = {
     },
     "gemm_wstream": {
         "kvb_gemm_wstream": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+        "kvb_gemm_wstream_gated": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
     },
     "gemm_tcgen05": {
         "kvb_gemm_tcgen05": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
@@ -512,11 +514,24 @@ class CudaKernels(KernelSet):
     def gate_up_act(self, x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, workspace, interleaved: bool,
                     activation: str = "silu", limit: float = 0.0) -> None:
         """out[M, I] = act(x Wg^T, x Wu^T) (see `silu_mul`); `w_gate_up` [2 I, K] holds gate and up rows one after the
-        other, or interleaved in eights (see csrc/gemm_skinny.cu).  The products with the activation in their epilogue
-        are built for silu; other activations take the product and the activation kernel."""
+        other, or interleaved in eights (see csrc/gemm_skinny.cu).  The clamped activation is in the epilogue of the two
+        weight-streaming products (steps of few rows); with more rows it takes the product and the activation kernel."""
         M, K = x.shape
         I = out.shape[1]
         if activation != "silu":
+            if activation != "clamped_swiglu" or not limit > 0.0:
+                raise KernelError(f"gate_up_act: activation '{activation}' (limit {limit}) is not built")
+            if interleaved and self._skinny(x.dtype, M, K, 2 * I):
+                self._count("gemm_skinny")
+                _check(self._gemm_skinny.kvb_gemm_skinny_gated(_dtype_code(out.dtype), _ptr(x), _ptr(w_gate_up), _ptr(out), M, 2 * I, K,
+                                                               float(limit), self._stream()), "gate_up_act (skinny, clamped)")
+                return
+            if interleaved and self._wstream(x.dtype, M, K):
+                self._count("gemm_wstream")
+                _check(self._gemm_ws.kvb_gemm_wstream_gated(_dtype_code(out.dtype), _ptr(x), _ptr(w_gate_up), _ptr(out), M, 2 * I, K,
+                                                            float(limit), _ptr(self.error_word), self._stream()),
+                       "gate_up_act (wstream, clamped)")
+                return
             gate_up = workspace.buffer("ffn.gate_up", (M, 2 * I), out.dtype)
             self.linear(x, w_gate_up, gate_up)
             self.silu_mul(gate_up, out, interleaved, activation, limit)

@@ -343,6 +343,27 @@ def test_clamped_gated_activation(kernels, dtype, interleaved):
     assert_close(got, ref, TOL[dtype])
 
 
+@pytest.mark.parametrize("M", [1, 8, 16, 24, 32, 200])
+def test_gated_product_with_the_clamped_activation_in_its_epilogue(kernels, M):
+    """bfloat16, gate and up rows interleaved in eights: up to 16 rows the register kernel, up to 32 the weight-streaming
+    tcgen05 kernel, beyond that product and activation kernel - all against the plain statement."""
+    from kvcache_b200.engine.workspace import Workspace
+    K, I, limit = 256, 320, 0.9
+    x = _rand(M, K, dtype=torch.bfloat16, seed=1)
+    gate, up = _rand(I, K, dtype=torch.bfloat16, seed=2, scale=0.1), _rand(I, K, dtype=torch.bfloat16, seed=3, scale=0.1)
+    w = torch.stack([gate.view(-1, 8, K), up.view(-1, 8, K)], dim=1).reshape(-1, K).contiguous()
+    ref, got = torch.zeros(M, I, dtype=torch.bfloat16), torch.zeros(M, I, dtype=torch.bfloat16, device=DEV)
+    TorchKernels(wide=True).gate_up_act(x, w, ref, None, True, "clamped_swiglu", limit)
+    before = dict(kernels.launch_counts)
+    kernels.gate_up_act(x.to(DEV), w.to(DEV), got, Workspace(DEV), True, activation="clamped_swiglu", limit=limit)
+    kernels.check_errors()
+    launched = {k: v - before.get(k, 0) for k, v in kernels.launch_counts.items() if v != before.get(k, 0)}
+    assert launched == ({"gemm_skinny": 1} if M <= 16 else {"gemm_wstream": 1} if M <= 32 else launched) and (M <= 32 or "silu_mul" in launched)
+    assert_close(got, ref, 2e-2)
+    g = (x.double() @ gate.double().t())
+    assert bool((g > limit).any()) and bool(((x.double() @ up.double().t()) < -limit).any())
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_pair_embedding(kernels, dtype):
     """Rows that open a portion take the slot's previous token, position 0 takes the table's last row, tokens that the
