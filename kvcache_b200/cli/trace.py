@@ -57,6 +57,8 @@ def main(argv=None) -> int:
         entries = []
         for item in record.get("entries", []):
             key = str(item["id"])
+            if not item["tokens"]:
+                continue                        # a request that brings nothing to this step
             if key not in slots:
                 slots[key] = core.cache.admit()
             entries.append(StepEntry(slots[key], item["tokens"], item.get("want", [])))
