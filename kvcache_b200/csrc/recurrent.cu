@@ -29,6 +29,13 @@ enum { SCAN_CHANNEL_DECAY = 0, SCAN_EXP_GATES = 1 };
 
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
+// One float from global into shared memory without a register in between; many can be in flight per thread.
+__device__ __forceinline__ void copy_async4(float* smem, const float* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+__device__ __forceinline__ void copy_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+
 // Scratch of the chunked form; chunk ids count the chunks of all segments in the order of the segments.
 struct ScanChunks {
     int L, S;              // tokens in a chunk; segments in the step
@@ -94,11 +101,34 @@ __global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 512 : 128) matrix_sta
     pdl_wait();
     pdl_launch_dependents();
     __shared__ float gate_s[3][SCAN_TILE], max_s[SCAN_TILE + 1], carry_s[2];     // exponential gates: see the loop
+    // Two staging buffers: while a tile of 32 tokens is computed, the next one's rows are already on their way
+    // (asynchronous copies of 4 bytes: the rows' columns start anywhere).  q is staged as it is and the read-out is
+    // multiplied by q_scale afterwards.  Key channels beyond D and value channels beyond Dv are zeroed once.
     extern __shared__ __align__(16) float tile_s[];
-    float* q_s = tile_s;                                       // [tile][RK], already times q_scale
-    float* k_s = q_s + SCAN_TILE * RK;                         // [tile][RK]
-    float* a_s = k_s + SCAN_TILE * RK;                         // [tile][RK], channel-decay form only
-    float* v_s = a_s + (MODE == SCAN_CHANNEL_DECAY ? SCAN_TILE * RK : 0);   // [tile][VC]
+    constexpr int PARTS = MODE == SCAN_CHANNEL_DECAY ? 3 : 2;
+    const int tile_floats = SCAN_TILE * (PARTS * RK + VC);
+    auto stage = [&](int which, int first_row, int rows) {
+        float* q_b = tile_s + (size_t)which * tile_floats;
+        float* k_b = q_b + SCAN_TILE * RK;
+        float* a_b = k_b + SCAN_TILE * RK;
+        float* v_b = q_b + SCAN_TILE * PARTS * RK;
+        for (int idx = threadIdx.x; idx < rows * D; idx += blockDim.x) {
+            const int row = idx / D, d = idx - row * D;
+            const float* src = proj + (size_t)(first_row + row) * P;
+            copy_async4(q_b + row * RK + d, src + q_col + h * D + d);
+            copy_async4(k_b + row * RK + d, src + k_col + h * D + d);
+            if (MODE == SCAN_CHANNEL_DECAY) copy_async4(a_b + row * RK + d, gate + (size_t)(first_row + row) * gate_stride + g0 + h * D + d);
+        }
+        const int v_cols = min(VC, Dv - (int)blockIdx.x * VC);
+        for (int idx = threadIdx.x; idx < rows * v_cols; idx += blockDim.x) {
+            const int row = idx / v_cols, c = idx - row * v_cols;
+            copy_async4(v_b + row * VC + c, proj + (size_t)(first_row + row) * P + v_col + h * Dv + blockIdx.x * VC + c);
+        }
+        copy_async_commit();
+    };
+    for (int idx = threadIdx.x; idx < 2 * tile_floats; idx += blockDim.x) tile_s[idx] = 0.f;
+    __syncthreads();
+    if (n_rows > 0) stage(0, r0, min(SCAN_TILE, n_rows));
     float S[R], nz[NPL], total[NPL];
     float* mem = memory + ((size_t)slot * H + h) * D * Dv;
     const size_t cid = (size_t)blockIdx.z * H + h;             // (chunk id, head) in the scratch arrays
@@ -129,19 +159,9 @@ __global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 512 : 128) matrix_sta
     for (int t = 0; t < n_rows; ++t) {
         const int r = r0 + t, tt = t % SCAN_TILE;
         if (tt == 0) {
-            __syncthreads();                                   // the tile before has been used up
-            const int rows = min(SCAN_TILE, n_rows - t);
-            for (int idx = threadIdx.x; idx < rows * RK; idx += blockDim.x) {
-                const int row = idx / RK, d = idx - row * RK;
-                const float* src = proj + (size_t)(r + row) * P;
-                q_s[idx] = d < D ? src[q_col + h * D + d] * q_scale : 0.f;
-                k_s[idx] = d < D ? src[k_col + h * D + d] : 0.f;
-                if (MODE == SCAN_CHANNEL_DECAY) a_s[idx] = d < D ? gate[(size_t)(r + row) * gate_stride + g0 + h * D + d] : 0.f;
-            }
-            for (int idx = threadIdx.x; idx < rows * VC; idx += blockDim.x) {
-                const int row = idx / VC, c = idx - row * VC;
-                v_s[idx] = blockIdx.x * VC + c < Dv ? proj[(size_t)(r + row) * P + v_col + h * Dv + blockIdx.x * VC + c] : 0.f;
-            }
+            copy_async_wait_all();
+            __syncthreads();                                   // this tile has landed, and the one before has been used up
+            if (t + SCAN_TILE < n_rows) stage(((t / SCAN_TILE) + 1) & 1, r + SCAN_TILE, min(SCAN_TILE, n_rows - t - SCAN_TILE));
             if (MODE == SCAN_EXP_GATES) {
                 // The gates of the tile's tokens, once for the block: thread j takes token t + j's two logarithms, the
                 // first thread walks the maximum through them, then thread j takes the token's three exponentials.
@@ -176,6 +196,10 @@ __global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 512 : 128) matrix_sta
             }
             __syncthreads();
         }
+        const float* q_s = tile_s + (size_t)((t / SCAN_TILE) & 1) * tile_floats;
+        const float* k_s = q_s + SCAN_TILE * RK;
+        const float* a_s = k_s + SCAN_TILE * RK;
+        const float* v_s = q_s + SCAN_TILE * PARTS * RK;
         const float4* q4 = reinterpret_cast<const float4*>(q_s + tt * RK + part * R);
         const float4* k4 = reinterpret_cast<const float4*>(k_s + tt * RK + part * R);
         const float4* a4 = reinterpret_cast<const float4*>(a_s + tt * RK + part * R);
@@ -192,12 +216,12 @@ __global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 512 : 128) matrix_sta
                 nz[i] = keep * nz[i] + take * k_s[tt * RK + d];
                 dot += nz[i] * q_s[tt * RK + d];
             }
-            if (PASS != SCAN_LOCAL) denom = 1.f / (fmaxf(fabsf(warp_sum(dot)), gate_s[2][tt]) + floor_);
+            if (PASS != SCAN_LOCAL) denom = 1.f / (fmaxf(fabsf(warp_sum(dot) * q_scale), gate_s[2][tt]) + floor_);
         } else if (PASS == SCAN_LOCAL && blockIdx.x == 0 && warp == 0) {
 #pragma unroll
             for (int i = 0; i < NPL; ++i) total[i] *= (lane + 32 * i < D) ? a_s[tt * RK + lane + 32 * i] : 1.f;
         }
-        float o = 0.f;
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;          // four chains of multiply-adds instead of one of R
 #pragma unroll
         for (int i = 0; i < R; i += 4) {
             const float4 kk = k4[i >> 2];
@@ -209,14 +233,16 @@ __global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 512 : 128) matrix_sta
             S[i + 2] = fmaf(aa.z, S[i + 2], kk.z * gain);
             S[i + 3] = fmaf(aa.w, S[i + 3], kk.w * gain);
             if (PASS != SCAN_LOCAL) {
-                o = fmaf(S[i], qq.x, o);
-                o = fmaf(S[i + 1], qq.y, o);
-                o = fmaf(S[i + 2], qq.z, o);
-                o = fmaf(S[i + 3], qq.w, o);
+                o0 = fmaf(S[i], qq.x, o0);
+                o1 = fmaf(S[i + 1], qq.y, o1);
+                o2 = fmaf(S[i + 2], qq.z, o2);
+                o3 = fmaf(S[i + 3], qq.w, o3);
             }
         }
         if (PASS == SCAN_LOCAL) continue;                      // the state only
+        float o = (o0 + o1) + (o2 + o3);
         if (KS == 2) o += __shfl_xor_sync(0xffffffffu, o, 1);
+        o *= q_scale;
         if (MODE == SCAN_EXP_GATES) o *= denom;
         if (part == 0 && col_ok) out[(size_t)r * H * Dv + h * Dv + col] = o;
     }
@@ -322,7 +348,7 @@ static void launch_scan(const float* proj, int P, int q_col, int k_col, int v_co
     // The exponential-gate form: all of a head's columns in one block.  The other: blocks of up to 4 warps.
     const int warps = MODE == SCAN_EXP_GATES ? total_warps : (total_warps < 4 ? total_warps : 4);
     const int col_blocks = (total_warps + warps - 1) / warps;
-    const size_t smem = (size_t)SCAN_TILE * ((MODE == SCAN_CHANNEL_DECAY ? 3 : 2) * R * KS + warps * COLS) * sizeof(float);
+    const size_t smem = 2 * (size_t)SCAN_TILE * ((MODE == SCAN_CHANNEL_DECAY ? 3 : 2) * R * KS + warps * COLS) * sizeof(float);
 #define KVB_SCAN_PASS(PASS, Z)                                                                                                  \
     do {                                                                                                                        \
         if (smem + 2048 > 48 * 1024)                                                                                            \
