@@ -76,13 +76,14 @@ constexpr int SCAN_TILE = 32;          // tokens staged at a time
 // block per head: its n and m are kept by every warp (lane l: key channels l, l + 32, ...; the same arithmetic, the same
 // bits), read at the start and written by the first warp at the end, with the loop's barriers in between.
 template <int MODE, int R, int KS, int PASS>
-__global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 512 : 128) matrix_state_scan_kernel(
+__global__ void __launch_bounds__(512) matrix_state_scan_kernel(
     const float* __restrict__ proj, int P, int q_col, int k_col, int v_col, const float* __restrict__ gate, int gate_stride,
     int g0, int g1, float p0, float q_scale, float floor_, const int* __restrict__ seg_q_start,
     const int* __restrict__ seg_q_len, const int* __restrict__ seg_slot, float* __restrict__ memory,
     float* __restrict__ normalizer, float* __restrict__ maximum, float* __restrict__ out, int H, int D, int Dv, ScanChunks ch) {
-    constexpr int RK = R * KS;                                 // key channels of a staged row, zero beyond D
-    constexpr int NPL = RK / 32;                               // normaliser entries a lane keeps
+    constexpr int RP = R + (KS > 1 ? 4 : 0);                   // a part's run in a staged row: 16 bytes of padding keep the parts' banks apart
+    constexpr int RKP = RP * KS;                               // a staged row of key channels, zero beyond D
+    constexpr int NPL = (R * KS + 31) / 32;                    // normaliser entries a lane keeps
     constexpr int COLS = 32 / KS;                              // columns of a warp
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const int h = blockIdx.y;
@@ -106,18 +107,20 @@ __global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 512 : 128) matrix_sta
     // multiplied by q_scale afterwards.  Key channels beyond D and value channels beyond Dv are zeroed once.
     extern __shared__ __align__(16) float tile_s[];
     constexpr int PARTS = MODE == SCAN_CHANNEL_DECAY ? 3 : 2;
-    const int tile_floats = SCAN_TILE * (PARTS * RK + VC);
+    const int tile_floats = SCAN_TILE * (PARTS * RKP + VC);
+    auto at = [](int d) { return (d / R) * RP + d % R; };      // where key channel d lies in a staged row
     auto stage = [&](int which, int first_row, int rows) {
         float* q_b = tile_s + (size_t)which * tile_floats;
-        float* k_b = q_b + SCAN_TILE * RK;
-        float* a_b = k_b + SCAN_TILE * RK;
-        float* v_b = q_b + SCAN_TILE * PARTS * RK;
+        float* k_b = q_b + SCAN_TILE * RKP;
+        float* a_b = k_b + SCAN_TILE * RKP;
+        float* v_b = q_b + SCAN_TILE * PARTS * RKP;
         for (int idx = threadIdx.x; idx < rows * D; idx += blockDim.x) {
             const int row = idx / D, d = idx - row * D;
             const float* src = proj + (size_t)(first_row + row) * P;
-            copy_async4(q_b + row * RK + d, src + q_col + h * D + d);
-            copy_async4(k_b + row * RK + d, src + k_col + h * D + d);
-            if (MODE == SCAN_CHANNEL_DECAY) copy_async4(a_b + row * RK + d, gate + (size_t)(first_row + row) * gate_stride + g0 + h * D + d);
+            copy_async4(q_b + row * RKP + at(d), src + q_col + h * D + d);
+            copy_async4(k_b + row * RKP + at(d), src + k_col + h * D + d);
+            if (MODE == SCAN_CHANNEL_DECAY)
+                copy_async4(a_b + row * RKP + at(d), gate + (size_t)(first_row + row) * gate_stride + g0 + h * D + d);
         }
         const int v_cols = min(VC, Dv - (int)blockIdx.x * VC);
         for (int idx = threadIdx.x; idx < rows * v_cols; idx += blockDim.x) {
@@ -197,12 +200,12 @@ __global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 512 : 128) matrix_sta
             __syncthreads();
         }
         const float* q_s = tile_s + (size_t)((t / SCAN_TILE) & 1) * tile_floats;
-        const float* k_s = q_s + SCAN_TILE * RK;
-        const float* a_s = k_s + SCAN_TILE * RK;
-        const float* v_s = q_s + SCAN_TILE * PARTS * RK;
-        const float4* q4 = reinterpret_cast<const float4*>(q_s + tt * RK + part * R);
-        const float4* k4 = reinterpret_cast<const float4*>(k_s + tt * RK + part * R);
-        const float4* a4 = reinterpret_cast<const float4*>(a_s + tt * RK + part * R);
+        const float* k_s = q_s + SCAN_TILE * RKP;
+        const float* a_s = k_s + SCAN_TILE * RKP;
+        const float* v_s = q_s + SCAN_TILE * PARTS * RKP;
+        const float4* q4 = reinterpret_cast<const float4*>(q_s + tt * RKP + part * RP);
+        const float4* k4 = reinterpret_cast<const float4*>(k_s + tt * RKP + part * RP);
+        const float4* a4 = reinterpret_cast<const float4*>(a_s + tt * RKP + part * RP);
         const float v = v_s[tt * VC + warp * COLS + lane / KS];
         float keep = 1.f, gain = v, denom = 1.f;
         if (MODE == SCAN_EXP_GATES) {
@@ -213,13 +216,15 @@ __global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 512 : 128) matrix_sta
 #pragma unroll
             for (int i = 0; i < NPL; ++i) {
                 const int d = lane + 32 * i;
-                nz[i] = keep * nz[i] + take * k_s[tt * RK + d];
-                dot += nz[i] * q_s[tt * RK + d];
+                if (d < D) {
+                    nz[i] = keep * nz[i] + take * k_s[tt * RKP + at(d)];
+                    dot += nz[i] * q_s[tt * RKP + at(d)];
+                }
             }
             if (PASS != SCAN_LOCAL) denom = 1.f / (fmaxf(fabsf(warp_sum(dot) * q_scale), gate_s[2][tt]) + floor_);
         } else if (PASS == SCAN_LOCAL && blockIdx.x == 0 && warp == 0) {
 #pragma unroll
-            for (int i = 0; i < NPL; ++i) total[i] *= (lane + 32 * i < D) ? a_s[tt * RK + lane + 32 * i] : 1.f;
+            for (int i = 0; i < NPL; ++i) total[i] *= (lane + 32 * i < D) ? a_s[tt * RKP + at(lane + 32 * i)] : 1.f;
         }
         float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;          // four chains of multiply-adds instead of one of R
 #pragma unroll
@@ -241,7 +246,8 @@ __global__ void __launch_bounds__(MODE == SCAN_EXP_GATES ? 512 : 128) matrix_sta
         }
         if (PASS == SCAN_LOCAL) continue;                      // the state only
         float o = (o0 + o1) + (o2 + o3);
-        if (KS == 2) o += __shfl_xor_sync(0xffffffffu, o, 1);
+        if (KS >= 2) o += __shfl_xor_sync(0xffffffffu, o, 1);
+        if (KS == 4) o += __shfl_xor_sync(0xffffffffu, o, 2);
         o *= q_scale;
         if (MODE == SCAN_EXP_GATES) o *= denom;
         if (part == 0 && col_ok) out[(size_t)r * H * Dv + h * Dv + col] = o;
@@ -339,16 +345,21 @@ __global__ void scan_chunk_starts_kernel(const int* __restrict__ seg_q_len, cons
 }
 
 template <int MODE, int R, int KS>
-static void launch_scan(const float* proj, int P, int q_col, int k_col, int v_col, const float* gate, int gate_stride, int g0, int g1,
+static int launch_scan(const float* proj, int P, int q_col, int k_col, int v_col, const float* gate, int gate_stride, int g0, int g1,
                         float p0, float q_scale, float floor_, const int* seg_q_start, const int* seg_q_len, const int* seg_slot,
                         float* memory, float* normalizer, float* maximum, float* out, int S, int H, int D, int Dv, ScanChunks ch,
                         int max_chunks, cudaStream_t stream) {
     constexpr int COLS = 32 / KS;
+    constexpr int RKP = (R + (KS > 1 ? 4 : 0)) * KS;
     const int total_warps = (Dv + COLS - 1) / COLS;
-    // The exponential-gate form: all of a head's columns in one block.  The other: blocks of up to 4 warps.
-    const int warps = MODE == SCAN_EXP_GATES ? total_warps : (total_warps < 4 ? total_warps : 4);
+    // The exponential-gate form: all of a head's columns in one block (the caller chose KS so that they are at most 16
+    // warps).  The other: blocks of up to 16 warps, fewer where the staging buffers would not fit.
+    int warps = MODE == SCAN_EXP_GATES ? total_warps : (total_warps < 16 ? total_warps : 16);
+    auto bytes = [&](int w) { return 2 * (size_t)SCAN_TILE * ((MODE == SCAN_CHANNEL_DECAY ? 3 : 2) * RKP + w * COLS) * sizeof(float); };
+    if (MODE == SCAN_CHANNEL_DECAY)
+        while (warps > 1 && bytes(warps) > 200 * 1024) warps >>= 1;
     const int col_blocks = (total_warps + warps - 1) / warps;
-    const size_t smem = 2 * (size_t)SCAN_TILE * ((MODE == SCAN_CHANNEL_DECAY ? 3 : 2) * R * KS + warps * COLS) * sizeof(float);
+    const size_t smem = bytes(warps);
 #define KVB_SCAN_PASS(PASS, Z)                                                                                                  \
     do {                                                                                                                        \
         if (smem + 2048 > 48 * 1024)                                                                                            \
@@ -357,19 +368,21 @@ static void launch_scan(const float* proj, int P, int q_col, int k_col, int v_co
                    q_col, k_col, v_col, gate, gate_stride, g0, g1, p0, q_scale, floor_, seg_q_start, seg_q_len, seg_slot, memory,    \
                    normalizer, maximum, out, H, D, Dv, ch);                                                                     \
     } while (0)
+    if (smem > 220 * 1024 || warps > 16) return KVB_ERR_LIMIT;
     if (max_chunks <= 0) {
         ScanChunks whole = {};
         whole.L = 1 << 30;
         whole.S = S;
         ch = whole;
         KVB_SCAN_PASS(SCAN_FROM_START, S);
-        return;
+        return KVB_OK;
     }
     KVB_SCAN_PASS(SCAN_LOCAL, max_chunks);
     kvb_launch(scan_chunk_starts_kernel<MODE>, dim3((D * Dv + 255) / 256, H, S), dim3(256), 0, stream, seg_q_len, seg_slot, (const float*)memory,
                (const float*)normalizer, (const float*)maximum, H, D, Dv, ch);
     KVB_SCAN_PASS(SCAN_FROM_START, max_chunks);
 #undef KVB_SCAN_PASS
+    return KVB_OK;
 }
 
 // proj: float32 [T, P] with q at q_col (H * D numbers), k at k_col, v at v_col (H * Dv).  `gate`: float32 rows of
@@ -384,8 +397,7 @@ KVB_API int kvb_matrix_state_scan(int mode, const float* proj, int P, int q_col,
                                   cudaStream_t stream) {
     if (S <= 0) return KVB_OK;
     if (H < 1 || D < 1 || Dv < 1 || (mode != SCAN_CHANNEL_DECAY && mode != SCAN_EXP_GATES)) return KVB_ERR_SHAPE;
-    // A block of the exponential-gate form holds all of a head's columns: at most 16 warps.
-    if (D > 256 || H > 65535 || S > 65535 || max_chunks > 65535 || Dv > (D > 128 ? 256 : 512)) return KVB_ERR_LIMIT;
+    if (D > 256 || Dv > 512 || H > 65535 || S > 65535 || max_chunks > 65535) return KVB_ERR_LIMIT;
     if (max_chunks > 0 && (chunk_len < 1 || scratch == nullptr)) return KVB_ERR_SHAPE;
     ScanChunks ch = {};
     if (max_chunks > 0) {
@@ -408,17 +420,33 @@ KVB_API int kvb_matrix_state_scan(int mode, const float* proj, int P, int q_col,
         if (blocks > most) blocks = most;
         kvb_launch(channel_decay_kernel, dim3((int)blocks), dim3(256), 0, stream, const_cast<float*>(gate), total, p0);
     }
+    // A column's key channels over KS lanes, so that a lane holds at most 64 of them (measured at 128 key channels: 64 a
+    // lane took 312 us where 128 took 489 and 32 took 475; at 64 key channels one lane a column 129 us, four 160);
+    // fewer lanes where the exponential-gate form's block (all of a head's columns) would pass 16 warps.
+    int ks = D <= 64 ? 1 : D <= 128 ? 2 : 4;
+    if (mode == SCAN_EXP_GATES)
+        while (ks > 1 && (Dv + 32 / ks - 1) / (32 / ks) > 16) ks >>= 1;
+    const int per_lane = (D + ks - 1) / ks;
+    const int r = per_lane <= 16 ? 16 : per_lane <= 32 ? 32 : per_lane <= 64 ? 64 : 128;
+    if (per_lane > 128) return KVB_ERR_LIMIT;
+    int rc = KVB_ERR_LIMIT;
 #define KVB_SCAN(MODE, R, KS)                                                                                                  \
-    launch_scan<MODE, R, KS>(proj, P, q_col, k_col, v_col, gate, gate_stride, g0, g1, p0, q_scale, floor_, seg_q_start,        \
-                             seg_q_len, seg_slot, memory, normalizer, maximum, out, S, H, D, Dv, ch, max_chunks, stream)
+    rc = launch_scan<MODE, R, KS>(proj, P, q_col, k_col, v_col, gate, gate_stride, g0, g1, p0, q_scale, floor_, seg_q_start,   \
+                                  seg_q_len, seg_slot, memory, normalizer, maximum, out, S, H, D, Dv, ch, max_chunks, stream)
+#define KVB_SCAN_KS(MODE, R)                                                                                                   \
+    do {                                                                                                                      \
+        if (ks == 4) KVB_SCAN(MODE, R, 4); else if (ks == 2) KVB_SCAN(MODE, R, 2); else KVB_SCAN(MODE, R, 1);                 \
+    } while (0)
 #define KVB_SCAN_SIZE(MODE)                                                                                                    \
     do {                                                                                                                      \
-        if (D <= 32) KVB_SCAN(MODE, 32, 1); else if (D <= 64) KVB_SCAN(MODE, 64, 1);                                          \
-        else if (D <= 128) KVB_SCAN(MODE, 128, 1); else KVB_SCAN(MODE, 128, 2);                                               \
+        if (r == 16) KVB_SCAN_KS(MODE, 16); else if (r == 32) KVB_SCAN_KS(MODE, 32);                                          \
+        else if (r == 64) KVB_SCAN_KS(MODE, 64); else KVB_SCAN_KS(MODE, 128);                                                 \
     } while (0)
     if (mode == SCAN_CHANNEL_DECAY) KVB_SCAN_SIZE(SCAN_CHANNEL_DECAY); else KVB_SCAN_SIZE(SCAN_EXP_GATES);
 #undef KVB_SCAN_SIZE
+#undef KVB_SCAN_KS
 #undef KVB_SCAN
+    if (rc != KVB_OK) return rc;
     return kvb_launch_status();
 }
 
